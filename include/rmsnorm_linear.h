@@ -1,0 +1,94 @@
+/* C ABI of librmsnorm_linear: fused RMSNorm -> Linear on NVIDIA B200 (sm_100a).
+ *
+ *     y[m, n] = rsqrt(mean_k x[m,k]^2 + eps) * sum_k x[m,k] * gamma[k] * W[n,k]
+ *
+ * Every entry point takes plain pointers and sizes; device pointers belong to
+ * the caller, the library never allocates, frees or keeps device memory, and
+ * every launch is asynchronous on the stream that is passed in.  All functions
+ * return 0 on success or a negative RL_ERR_* code; nothing throws.
+ *
+ * Each function names the interface of the reference project
+ * (dungwoong/kernel-benchmarking) that it stands in for.
+ */
+#ifndef RMSNORM_LINEAR_H_
+#define RMSNORM_LINEAR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  RL_OK = 0,
+  RL_ERR_NULL_POINTER = -1,     /* a required pointer is NULL */
+  RL_ERR_BAD_SHAPE = -2,        /* M, N or K <= 0, or a leading dimension smaller than the row */
+  RL_ERR_ALIGNMENT = -3,        /* K or a leading dimension not a multiple of 8 (16 for e4m3) elements, or a pointer not 16-byte aligned */
+  RL_ERR_BAD_DTYPE = -4,        /* unknown weight dtype code */
+  RL_ERR_WORKSPACE = -5,        /* workspace missing or smaller than rl_workspace_bytes() */
+  RL_ERR_UNSUPPORTED_ARCH = -6, /* current device is not compute capability 10.x */
+  RL_ERR_BAD_VARIANT = -7,      /* unknown kernel variant, or one that cannot run this shape */
+  RL_ERR_TENSOR_MAP = -8,       /* the driver rejected a TMA descriptor */
+  RL_ERR_DEVICE_TIMEOUT = -9,   /* a bounded wait inside a kernel ran out (reported by rl_read_status) */
+  RL_ERR_CUDA = -1000           /* RL_ERR_CUDA - cudaError_t of the failing runtime call */
+};
+
+/* weight dtype codes */
+enum { RL_W_BF16 = 0, RL_W_E4M3 = 1 };
+
+/* kernel variants (0 picks by shape) */
+enum {
+  RL_VARIANT_AUTO = 0,
+  RL_VARIANT_PREFILL_TS_N192 = 1,  /* gamma-folded activations handed to the MMA through tensor memory */
+  RL_VARIANT_PREFILL_SS_N192 = 2,  /* gamma folded in place in shared memory */
+  RL_VARIANT_PREFILL_SS_N256 = 3,
+  RL_VARIANT_PREFILL_TS_N128 = 4,
+  RL_VARIANT_PREFILL_SS_N128 = 5,
+  RL_VARIANT_DECODE = 20           /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
+};
+
+/* Library version (major * 1000 + minor).  No reference counterpart. */
+int rl_version(void);
+
+/* Text for an RL_ERR_* code.  Stands in for the exception text of the
+ * reference's native extension (third_party/cublas_gemm/python/ext_kernel.cu:10-22). */
+const char* rl_error_string(int code);
+
+/* Bytes of caller-provided workspace a call with this shape needs (status
+ * block, and for M <= 64 the split-K partial tiles and tile counters).  Pure
+ * arithmetic, needs no GPU.  No reference counterpart (the reference's kernels
+ * allocate through their DSL runtimes). */
+size_t rl_workspace_bytes(int M, int N, int K, int w_dtype);
+
+/* Zero the workspace (status block and tile counters) on `stream`.  Must run
+ * once before the first use of a workspace; kernels leave it clean afterwards. */
+int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* bf16 fused RMSNorm -> Linear.
+ *   x [M, K] bf16 row-major (leading dimension ldx elements), gamma [K] bf16 or
+ *   NULL (= ones, the reference's semantics), W [N, K] bf16 row-major (ldw),
+ *   y [M, N] bf16 row-major (ldy), fp32 accumulation.
+ * Replaces, for this path, the reference's kernel callables
+ *   torch_kernel(a, b, eps)                      demo/rmsnorm_linear.py:36-38
+ *   baselines.rmsnorm_linear(a, b, eps)          python/baselines/rmsnorm_swiglu.py:28-34
+ *   rmsnorm_lin_kernel(x, y, eps)                python/bench_kernels/helion/rmsnorm_linear.py:5-35
+ *   rmsnorm_matmul_persistent(X, W, eps, ...)    python/bench_kernels/tilelang/tilelang_rmsnorm_linear.py:7-87
+ *   compiled_gemm(a, b, o, eps)                  demo/rmsnorm_linear.py:65-68
+ * `workspace` may be NULL for M > 64 (then device-side timeouts go unreported). */
+int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void* y,
+                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
+                           float eps, void* workspace, size_t workspace_bytes,
+                           int variant, void* stream);
+
+/* Read the status block of a workspace (synchronises the stream's device: use
+ * outside the hot loop).  Returns RL_OK or RL_ERR_DEVICE_TIMEOUT; when `detail`
+ * is not NULL it receives 8 ints: code, role, barrier, block, index, parity, 0, 0.
+ * Stands in for the reference's CUDA_CHECK after a launch
+ * (third_party/cublas_gemm/cublas_gemm.cu:17-29). */
+int rl_read_status(const void* workspace, int* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RMSNORM_LINEAR_H_ */

@@ -1,0 +1,9 @@
+"""Fused RMSNorm -> Linear for NVIDIA B200 (sm_100a): hand-written CUDA behind a C ABI.
+
+`rmsnorm_linear(x, gamma, W, eps) -> y` keeps the call surface of the kernels that
+dungwoong/kernel-benchmarking profiles (demo/rmsnorm_linear.py).  There is no CPU
+or PyTorch fallback: the compiled library must be present.
+"""
+from .ops import check_status, rmsnorm_linear  # noqa: F401
+
+__all__ = ["rmsnorm_linear", "check_status"]

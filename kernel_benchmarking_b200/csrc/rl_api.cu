@@ -1,0 +1,242 @@
+// C ABI of librmsnorm_linear: argument checks, TMA descriptors, kernel choice.
+// Declarations and the reference interfaces they replace: include/rmsnorm_linear.h
+#include "../../include/rmsnorm_linear.h"
+
+#include <mutex>
+
+#include "rl_decode.cuh"
+#include "rl_prefill.cuh"
+
+namespace {
+
+using namespace rl;
+
+constexpr int RL_MAX_CTAS = 160;      // upper bound on the persistent grid (B200: 148 SMs)
+constexpr size_t STATUS_BYTES = 256;  // RL_STATUS_INTS ints
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline int cuda_err(cudaError_t e) { return RL_ERR_CUDA - (int)e; }
+
+// ---- driver entry point for cuTensorMapEncodeTiled (no link-time libcuda dependency)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+// Row-major 2-D tensor [outer, inner] of 1- or 2-byte elements, 128-byte-swizzled boxes.
+int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, uint64_t inner,
+             uint64_t outer, uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return RL_ERR_TENSOR_MAP;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_elems * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RL_OK : RL_ERR_TENSOR_MAP;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+  int cc_major = 0;
+  bool ok = false;
+};
+int device_info(DeviceInfo* out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_err(e);
+  if (dev < 0 || dev >= 64) return RL_ERR_UNSUPPORTED_ARCH;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cache[dev].ok) {
+    if ((e = cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+      return cuda_err(e);
+    if ((e = cudaDeviceGetAttribute(&cache[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+      return cuda_err(e);
+    cache[dev].ok = true;
+  }
+  *out = cache[dev];
+  return RL_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct WsLayout {
+  size_t counters_off, ssq_off, partials_off, total;
+};
+WsLayout ws_layout(int M, int N) {
+  WsLayout w{};
+  if (M > 64) {
+    w.total = STATUS_BYTES;
+    return w;
+  }
+  const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const size_t n_tiles = (size_t)(N + 127) / 128;
+  w.counters_off = STATUS_BYTES;
+  w.ssq_off = w.counters_off + align_up(n_tiles * 4, 256);
+  w.partials_off = w.ssq_off + align_up((size_t)RL_MAX_CTAS * 2 * mpad * 4, 256);
+  w.total = w.partials_off + (size_t)RL_MAX_CTAS * 2 * mpad * 128 * 4;
+  return w;
+}
+
+template <class Cfg>
+int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
+                   int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st) {
+  CUtensorMap tx, tw, ty;
+  int rc;
+  if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
+  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, N, ldw, 64, Cfg::BN))) return rc;
+  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
+  PrefillParams p{};
+  p.M = M; p.N = N; p.K = K; p.eps = eps;
+  p.gamma = gamma;
+  p.m_tiles = (M + 127) / 128;
+  p.n_tiles = (N + Cfg::BN - 1) / Cfg::BN;
+  p.group_m = 16;
+  p.status = status;
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  cudaError_t e = cudaFuncSetAttribute(prefill_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_err(e);
+  prefill_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
+template <class Cfg>
+int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
+                  int64_t ldx, int64_t ldw, int64_t ldy, float eps, uint8_t* ws, const WsLayout& wl, int sms,
+                  cudaStream_t st) {
+  CUtensorMap tw, tx;
+  int rc;
+  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, N, ldw, 64, 128))) return rc;
+  if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, Cfg::MPAD))) return rc;
+  DecodeParams p{};
+  p.M = M; p.N = N; p.K = K; p.eps = eps;
+  p.gamma = gamma;
+  p.y = reinterpret_cast<__nv_bfloat16*>(y);
+  p.ldy = ldy;
+  p.n_tiles = (N + 127) / 128;
+  p.KB = (K + 63) / 64;
+  const long long units = (long long)p.n_tiles * p.KB;
+  if (units > 0x7fffffffLL) return RL_ERR_BAD_SHAPE;
+  p.units_total = (int)units;
+  p.status = reinterpret_cast<int*>(ws);
+  p.counters = reinterpret_cast<int*>(ws + wl.counters_off);
+  p.ssq_partials = reinterpret_cast<float*>(ws + wl.ssq_off);
+  p.partials = reinterpret_cast<float*>(ws + wl.partials_off);
+  int grid = sms < RL_MAX_CTAS ? sms : RL_MAX_CTAS;
+  if (units < grid) grid = (int)units;
+  cudaError_t e = cudaFuncSetAttribute(decode_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_err(e);
+  decode_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tw, tx, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
+}  // namespace
+
+extern "C" {
+
+int rl_version(void) { return 1000; }
+
+const char* rl_error_string(int code) {
+  switch (code) {
+    case RL_OK: return "ok";
+    case RL_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case RL_ERR_BAD_SHAPE: return "M, N and K must be positive and leading dimensions must cover a row";
+    case RL_ERR_ALIGNMENT:
+      return "K and the leading dimensions must be multiples of 8 elements (16 for e4m3) and pointers 16-byte aligned";
+    case RL_ERR_BAD_DTYPE: return "unknown weight dtype";
+    case RL_ERR_WORKSPACE: return "workspace missing or smaller than rl_workspace_bytes()";
+    case RL_ERR_UNSUPPORTED_ARCH: return "the current device is not an sm_100 (B200) GPU";
+    case RL_ERR_BAD_VARIANT: return "unknown kernel variant, or one that cannot run this shape";
+    case RL_ERR_TENSOR_MAP: return "the driver rejected a TMA descriptor";
+    case RL_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out of time";
+    default: break;
+  }
+  if (code <= RL_ERR_CUDA) return cudaGetErrorString((cudaError_t)(RL_ERR_CUDA - code));
+  return "unknown error code";
+}
+
+size_t rl_workspace_bytes(int M, int N, int K, int w_dtype) {
+  (void)K;
+  (void)w_dtype;
+  if (M <= 0 || N <= 0) return STATUS_BYTES;
+  return ws_layout(M, N).total;
+}
+
+int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return RL_ERR_NULL_POINTER;
+  if (workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, (cudaStream_t)stream);
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
+int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void* y, int M, int N, int K,
+                           int64_t ldx, int64_t ldw, int64_t ldy, float eps, void* workspace,
+                           size_t workspace_bytes, int variant, void* stream) {
+  if (!x || !W || !y) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (ldx & 7) || (ldw & 7) || !aligned16(x) || !aligned16(W) || (gamma && !aligned16(gamma)))
+    return RL_ERR_ALIGNMENT;
+  const bool decode = (variant == RL_VARIANT_DECODE) || (variant == RL_VARIANT_AUTO && M <= 64);
+  if (decode && M > 64) return RL_ERR_BAD_VARIANT;
+  if (!decode && ((ldy & 7) || !aligned16(y))) return RL_ERR_ALIGNMENT;
+  const WsLayout wl = ws_layout(decode ? M : 65, N);
+  if (decode && !workspace) return RL_ERR_WORKSPACE;
+  if (workspace && workspace_bytes < wl.total) return RL_ERR_WORKSPACE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  cudaStream_t st = (cudaStream_t)stream;
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  int* status = reinterpret_cast<int*>(workspace);
+
+  if (decode) {
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    if (M <= 16) return launch_decode<DecodeCfg<16, 10>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+    if (M <= 32) return launch_decode<DecodeCfg<32, 9>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+    return launch_decode<DecodeCfg<64, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+  }
+
+  if (variant == RL_VARIANT_AUTO) variant = RL_VARIANT_PREFILL_TS_N192;
+#define RL_PREFILL(BN, ST, AM) \
+  launch_prefill<PrefillCfg<BN, ST, AM>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
+  switch (variant) {
+    case RL_VARIANT_PREFILL_TS_N192: return RL_PREFILL(192, 4, A_TS_FOLD);
+    case RL_VARIANT_PREFILL_SS_N192: return g ? RL_PREFILL(192, 4, A_SS_FOLD) : RL_PREFILL(192, 4, A_SS_DIRECT);
+    case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD) : RL_PREFILL(256, 4, A_SS_DIRECT);
+    case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 6, A_TS_FOLD);
+    case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 6, A_SS_FOLD) : RL_PREFILL(128, 6, A_SS_DIRECT);
+    default: return RL_ERR_BAD_VARIANT;
+  }
+#undef RL_PREFILL
+}
+
+int rl_read_status(const void* workspace, int* detail) {
+  if (!workspace) return RL_ERR_NULL_POINTER;
+  int h[8] = {0};
+  cudaError_t e = cudaMemcpy(h, workspace, sizeof(h), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_err(e);
+  if (detail)
+    for (int i = 0; i < 8; ++i) detail[i] = h[i];
+  return h[0] == 0 ? RL_OK : RL_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

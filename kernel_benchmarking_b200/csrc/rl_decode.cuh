@@ -1,0 +1,356 @@
+// Fused RMSNorm -> Linear for M <= 64 tokens (HBM-bound on W).
+//
+// Operands are swapped so that the 128-wide UMMA M dimension runs over output
+// channels: A = W tile [128 channels x 64], B = (x*gamma) tile [MPAD tokens x 64],
+// D[channel, token] in TMEM.  The (channel-tile, k-block) units are dealt out
+// stream-K style: CTA c of G streams one contiguous run of units, so every SM
+// pulls the same share of W through a deep TMA ring.  A channel tile whose
+// k-range is split over several CTAs is finished by the last CTA to arrive:
+// every contributor writes its fp32 partial tile and its partial sum of
+// squares to the workspace and bumps the tile's counter; whoever sees the final
+// count adds the partials in contributor order (so the result does not depend
+// on arrival order), applies 1/rms per token and stores y.  No CTA ever waits
+// for another.  Counters are left at zero for the next launch.
+//
+// Warp roles: 0 TMA producer, 1 UMMA issuer, 2-5 transform (sum of squares via
+// warp shuffles + gamma fold in shared memory), 6-9 epilogue.
+#pragma once
+#include "rl_ptx.cuh"
+
+namespace rl {
+
+struct DecodeParams {
+  int M, N, K;
+  float eps;
+  const __nv_bfloat16* gamma;  // [K] or nullptr
+  __nv_bfloat16* y;
+  long long ldy;
+  int n_tiles, KB, units_total;
+  int* status;
+  int* counters;        // [n_tiles], zero between launches
+  float* partials;      // [grid][2][MPAD][128]
+  float* ssq_partials;  // [grid][2][MPAD]
+};
+
+template <int MPAD_, int STAGES_>
+struct DecodeCfg {
+  static constexpr int MPAD = MPAD_, STAGES = STAGES_;
+  static constexpr int THREADS = 320;
+  static constexpr int W_BYTES = 128 * 64 * 2;
+  static constexpr int X_BYTES = MPAD * 64 * 2;
+  static constexpr int G_BYTES = 128;
+  static constexpr int OFF_W = 0;
+  static constexpr int OFF_X = OFF_W + STAGES * W_BYTES;
+  static constexpr int OFF_G = OFF_X + STAGES * X_BYTES;
+  static constexpr int OFF_SSQ = OFF_G + STAGES * G_BYTES;
+  static constexpr int OFF_BAR = OFF_SSQ + 2 * MPAD * 4;
+  static constexpr int NUM_BARS = 3 * STAGES + 6;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
+  static constexpr int TMEM_COLS = (2 * MPAD < 32) ? 32 : 2 * MPAD;
+  static constexpr int NCH = MPAD / 16;  // 16-byte chunks of the x tile per transform thread
+  static_assert(MPAD == 16 || MPAD == 32 || MPAD == 64, "MPAD");
+  static_assert(X_BYTES % 1024 == 0, "x stage alignment");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+// Balanced contiguous split of `total` units over `G` CTAs.
+__host__ __device__ __forceinline__ int sk_begin(int c, int total, int G) {
+  const int q = total / G, rem = total % G;
+  return c * q + (c < rem ? c : rem);
+}
+__host__ __device__ __forceinline__ int sk_cta_of_unit(int u, int total, int G) {
+  const int q = total / G, rem = total % G;
+  const int cut = rem * (q + 1);
+  return (u < cut) ? u / (q + 1) : rem + (u - cut) / q;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+              const DecodeParams p) {
+  constexpr int MPAD = Cfg::MPAD, STAGES = Cfg::STAGES, NCH = Cfg::NCH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_xf = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+  auto bar_tfull = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };
+  auto bar_rs = [&](int a) { return bar0 + 8u * (3 * STAGES + 4 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_MISC);
+  volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
+  volatile int* epi_last = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 12);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
+  float* ssq = reinterpret_cast<float*>(smem + Cfg::OFF_SSQ);  // [2][MPAD]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = p.KB;
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int u_begin = sk_begin(cta, p.units_total, G);
+  const int u_end = sk_begin(cta + 1, p.units_total, G);
+  const bool has_gamma = (p.gamma != nullptr);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_xf(s), 4);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull(a), 1);
+      mbar_init(bar_tempty(a), 4);
+      mbar_init(bar_rs(a), 4);
+    }
+    ctl->abort = 0;
+    ctl->status = p.status;
+    fence_mbar_init();
+    prefetch_tmap(&tm_w);
+    prefetch_tmap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();  // W is streamed exactly once
+      const uint64_t pol_x = l2_policy_evict_last();   // x is re-read by every CTA
+      int s = 0;
+      uint32_t ph = 0;
+      int tile = u_begin / KB, kb = u_begin - tile * KB;
+      for (int u = u_begin; u < u_end; ++u) {
+        if (!mbar_wait(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, u)) break;
+        const int kvalid = min(64, p.K - kb * 64);
+        const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
+        mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
+        tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
+        tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
+        if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+        if (++kb == KB) { kb = 0; ++tile; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(128, MPAD, 1, 1);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int seg = 0;
+      for (int u = u_begin; ok && u < u_end; ++seg) {
+        const int tile = u / KB, kb0 = u - tile * KB;
+        const int n_units = min(KB - kb0, u_end - u);
+        const int acc = seg & 1;
+        const uint32_t aph = (seg >> 1) & 1;
+        if (!mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, seg)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * MPAD;
+        for (int i = 0; i < n_units; ++i) {
+          if (!mbar_wait(bar_full(s), ph, ctl, 1, s, u + i)) { ok = false; break; }
+          if (!mbar_wait(bar_xf(s), ph, ctl, 1, STAGES + s, u + i)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_W + s * Cfg::W_BYTES);
+          const uint64_t bdesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_X + s * Cfg::X_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+          umma_commit(bar_empty(s));
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(bar_tfull(acc));
+        u += n_units;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ transform
+    const int tt = threadIdx.x - 64;  // 0..127
+    const int c = tt & 7;             // 16-byte chunk within the 128-byte row
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    int seg = 0;
+    for (int u = u_begin; ok && u < u_end; ++seg) {
+      const int tile = u / KB, kb0 = u - tile * KB;
+      const int n_units = min(KB - kb0, u_end - u);
+      const int acc = seg & 1;
+      const uint32_t aph = (seg >> 1) & 1;
+      float ss[NCH];
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) ss[i] = 0.f;
+      for (int i = 0; i < n_units; ++i) {
+        ok = mbar_wait(bar_full(s), ph, ctl, 2, s, u + i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        uint8_t* xt = smem + Cfg::OFF_X + s * Cfg::X_BYTES;
+        const int kvalid = p.K - (kb0 + i) * 64;
+        uint4 gv = make_uint4(0, 0, 0, 0);
+        const bool cvalid = (c * 8 < kvalid);
+        if (has_gamma && cvalid) gv = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES)[c];
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int row = (tt >> 3) + j * 16;
+          uint4* ptr = reinterpret_cast<uint4*>(xt + row * 128 + ((c ^ (row & 7)) << 4));
+          uint4 v = *ptr;
+          float a = ss[j];
+          a = fmaf(bf16lo(v.x), bf16lo(v.x), a); a = fmaf(bf16hi(v.x), bf16hi(v.x), a);
+          a = fmaf(bf16lo(v.y), bf16lo(v.y), a); a = fmaf(bf16hi(v.y), bf16hi(v.y), a);
+          a = fmaf(bf16lo(v.z), bf16lo(v.z), a); a = fmaf(bf16hi(v.z), bf16hi(v.z), a);
+          a = fmaf(bf16lo(v.w), bf16lo(v.w), a); a = fmaf(bf16hi(v.w), bf16hi(v.w), a);
+          ss[j] = a;
+          if (has_gamma) {
+            if (cvalid) {
+              v.x = mul_bf16x2(v.x, gv.x); v.y = mul_bf16x2(v.y, gv.y);
+              v.z = mul_bf16x2(v.z, gv.z); v.w = mul_bf16x2(v.w, gv.w);
+            } else {
+              v = make_uint4(0, 0, 0, 0);
+            }
+            *ptr = v;
+          }
+        }
+        if (has_gamma) fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_xf(s));
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+      if (!ok) break;
+      // each token row is spread over 8 neighbouring lanes: butterfly-reduce
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        float a = ss[j];
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        ss[j] = a;
+      }
+      ok = mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 2, 3 * STAGES + 2 + acc, seg);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (c == 0) {
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) ssq[acc * MPAD + (tt >> 3) + j * 16] = ss[j];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_rs(acc));
+      u += n_units;
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 192;
+    const float inv_k = 1.0f / (float)p.K;
+    int seg = 0;
+    for (int u = u_begin; u < u_end; ++seg) {
+      const int tile = u / KB, kb0 = u - tile * KB;
+      const int n_units = min(KB - kb0, u_end - u);
+      const int acc = seg & 1;
+      const uint32_t aph = (seg >> 1) & 1;
+      mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, seg) &&
+          mbar_wait(bar_rs(acc), aph, ctl, 3, 3 * STAGES + 4 + acc, seg);
+      // named barriers have no time limit: one thread decides for the whole group
+      named_bar_sync(3, 128);
+      if (epi_tid == 0) *epi_go = ctl->abort ? 0 : 1;
+      named_bar_sync(4, 128);
+      if (*epi_go == 0) break;
+      tc_fence_after();
+
+      float a[MPAD];
+#pragma unroll
+      for (int h = 0; h < MPAD / 16; ++h) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + acc * MPAD + h * 16, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) a[h * 16 + j] = __uint_as_float(v[j]);
+      }
+      const int n = tile * 128 + n_local;
+      const bool whole = (n_units == KB);
+      bool finish = whole;
+      if (!whole) {
+        const int slot = (seg == 0) ? 0 : 1;
+        float* part = p.partials + (size_t)(cta * 2 + slot) * MPAD * 128;
+#pragma unroll
+        for (int m = 0; m < MPAD; ++m) part[m * 128 + n_local] = a[m];
+        if (epi_tid < MPAD) p.ssq_partials[(cta * 2 + slot) * MPAD + epi_tid] = ssq[acc * MPAD + epi_tid];
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (epi_tid == 0) {
+          const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
+          const int last = sk_cta_of_unit(tile * KB + KB - 1, p.units_total, G);
+          const int old = atomicAdd(p.counters + tile, 1);
+          const int is_last = (old == last - first);
+          if (is_last) p.counters[tile] = 0;  // ready for the next launch
+          *epi_last = is_last;
+          __threadfence();
+        }
+        named_bar_sync(2, 128);
+        finish = (*epi_last != 0);
+      }
+      if (finish) {
+        if (!whole) {
+          const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
+          const int last = sk_cta_of_unit(tile * KB + KB - 1, p.units_total, G);
+#pragma unroll
+          for (int m = 0; m < MPAD; ++m) a[m] = 0.f;
+          for (int cc = first; cc <= last; ++cc) {
+            const int cslot = (sk_begin(cc, p.units_total, G) / KB == tile) ? 0 : 1;
+            const float* part = p.partials + (size_t)(cc * 2 + cslot) * MPAD * 128;
+#pragma unroll
+            for (int m = 0; m < MPAD; ++m) a[m] += __ldcg(part + m * 128 + n_local);
+          }
+#pragma unroll
+          for (int m = 0; m < MPAD; ++m) {
+            if (m < p.M) {
+              float s2 = 0.f;
+              for (int cc = first; cc <= last; ++cc) {
+                const int cslot = (sk_begin(cc, p.units_total, G) / KB == tile) ? 0 : 1;
+                s2 += __ldcg(p.ssq_partials + (cc * 2 + cslot) * MPAD + m);
+              }
+              const float r = 1.0f / sqrtf(s2 * inv_k + p.eps);
+              if (n < p.N) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * r);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < MPAD; ++m) {
+            if (m < p.M) {
+              const float r = 1.0f / sqrtf(ssq[acc * MPAD + m] * inv_k + p.eps);
+              if (n < p.N) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * r);
+            }
+          }
+        }
+      }
+      // accumulator and ssq[acc] fully consumed
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty(acc));
+      u += n_units;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (ctl->abort) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace rl

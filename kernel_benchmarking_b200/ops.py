@@ -1,0 +1,105 @@
+"""`rmsnorm_linear(x, gamma, W, eps) -> y` on torch tensors: the reference's kernel call surface.
+
+The reference registers a kernel as any callable `fn(a, b, eps) -> out[M, N]`
+on bf16 CUDA tensors a [M, K], b [N, K] (demo/new_profiling/rmsnorm_linear_new.py:97-103,
+python/baselines/rmsnorm_swiglu.py:28-34).  This module provides that callable on
+top of the C ABI; PyTorch only supplies device memory and the current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(device: torch.device, nbytes: int, stream: int) -> torch.Tensor:
+    """Per (device, stream) scratch for the status block and split-K partials; grown on demand,
+    zeroed once by the library when created."""
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 12), dtype=torch.uint8, device=device)
+        _lib.check(_lib.load().rl_workspace_init(ws.data_ptr(), ws.numel(), stream), "rl_workspace_init")
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_matrix(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this operator has no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must be row-major with unit stride along its last dimension")
+
+
+def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tensor, eps: float = 1e-6, *,
+                   out: Optional[torch.Tensor] = None, variant: str | int = "auto") -> torch.Tensor:
+    """y = rms_norm(x, weight=gamma, eps) @ W.t() in one fused sm_100a kernel.
+
+    x [M, K] bf16, gamma [K] bf16 or None (None = ones, which is the reference operator:
+    `F.rms_norm(a, (K,), eps=eps) @ b.t()`, demo/rmsnorm_linear.py:36-38), W [N, K] bf16.
+    Returns y [M, N] bf16 (fp32 accumulation).  Runs on the current CUDA stream, asynchronously.
+    """
+    _check_matrix("x", x, torch.bfloat16)
+    _check_matrix("W", W, torch.bfloat16)
+    M, K = x.shape
+    N, K2 = W.shape
+    if K2 != K:
+        raise ValueError(f"x is [M, {K}] but W is [N, {K2}]: inner dimensions differ")
+    if W.device != x.device:
+        raise ValueError("x and W must be on the same device")
+    if gamma is not None:
+        if not gamma.is_cuda or gamma.device != x.device or gamma.dtype != torch.bfloat16:
+            raise ValueError("gamma must be a bf16 CUDA tensor on x's device")
+        if gamma.dim() != 1 or gamma.shape[0] != K or gamma.stride(0) != 1:
+            raise ValueError(f"gamma must be a contiguous vector of length K={K}")
+    if M == 0 or N == 0:
+        return torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        ldy = (N + 7) // 8 * 8  # rows of y start on 16-byte boundaries for the TMA store
+        buf = torch.empty((M, ldy), dtype=torch.bfloat16, device=x.device)
+        out = buf if ldy == N else buf[:, :N]
+    else:
+        _check_matrix("out", out, torch.bfloat16)
+        if tuple(out.shape) != (M, N) or out.device != x.device:
+            raise ValueError(f"out must be [{M}, {N}] on x's device")
+    v = _lib.VARIANTS[variant] if isinstance(variant, str) else int(variant)
+    lib = _lib.load()
+    stream = _stream_ptr()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16), stream)
+        rc = lib.rl_rmsnorm_linear_bf16(
+            x.data_ptr(), None if gamma is None else gamma.data_ptr(), W.data_ptr(), out.data_ptr(),
+            M, N, K, x.stride(0), W.stride(0), out.stride(0), ctypes.c_float(eps),
+            ws.data_ptr(), ws.numel(), v, stream)
+    _lib.check(rc, "rl_rmsnorm_linear_bf16")
+    return out
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel launched through this module recorded a device-side
+    timeout.  Kept out of `rmsnorm_linear` so the hot call never synchronises."""
+    lib = _lib.load()
+    for (dev, _stream), ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, dev):
+            continue
+        detail = (ctypes.c_int * 8)()
+        with torch.cuda.device(dev):
+            torch.cuda.synchronize()
+            rc = lib.rl_read_status(ws.data_ptr(), detail)
+        if rc != _lib.RL_OK:
+            raise RuntimeError(f"rmsnorm_linear: {_lib.error_string(rc)}; detail={list(detail)}")
