@@ -13,6 +13,11 @@ using namespace rl;
 
 constexpr int RL_MAX_CTAS = 160;      // upper bound on the persistent grid (B200: 148 SMs)
 constexpr size_t STATUS_BYTES = 256;  // RL_STATUS_INTS ints
+// The tile counters must be zero between launches and kernels leave them so, but only if
+// every shape finds them at the same place: the counter region has a fixed capacity and
+// position, whatever M, N and K are.  Partial tiles behind it need no clean state.
+constexpr int RL_MAX_DECODE_TILES = 16384;  // N <= 2,097,152 output channels
+constexpr size_t COUNTER_BYTES = (size_t)RL_MAX_DECODE_TILES * 4;
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int cuda_err(cudaError_t e) { return RL_ERR_CUDA - (int)e; }
@@ -83,9 +88,9 @@ WsLayout ws_layout(int M, int N) {
     return w;
   }
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  const size_t n_tiles = (size_t)(N + 127) / 128;
+  (void)N;
   w.counters_off = STATUS_BYTES;
-  w.ssq_off = w.counters_off + align_up(n_tiles * 4, 256);
+  w.ssq_off = w.counters_off + COUNTER_BYTES;
   w.partials_off = w.ssq_off + align_up((size_t)RL_MAX_CTAS * 2 * mpad * 4, 256);
   w.total = w.partials_off + (size_t)RL_MAX_CTAS * 2 * mpad * 128 * 4;
   return w;
@@ -130,6 +135,7 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   p.y = reinterpret_cast<__nv_bfloat16*>(y);
   p.ldy = ldy;
   p.n_tiles = (N + 127) / 128;
+  if (p.n_tiles > RL_MAX_DECODE_TILES) return RL_ERR_BAD_SHAPE;
   p.KB = (K + 63) / 64;
   const long long units = (long long)p.n_tiles * p.KB;
   if (units > 0x7fffffffLL) return RL_ERR_BAD_SHAPE;

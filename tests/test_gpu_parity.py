@@ -1,0 +1,198 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the CPU oracle and the golden vectors.
+
+Tolerances (max|y - y_ref| / max|y_ref|, y_ref = the reference's torch path on the widened inputs):
+bf16 path <= 1e-2.  Everything here needs a B200 and the compiled library.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_benchmarking_b200 as kb
+from kernel_benchmarking_b200 import _lib
+from oracle import rmsnorm_linear_oracle as orc
+
+pytestmark = pytest.mark.gpu
+BF16_TOL = 1e-2
+DEV = "cuda:0"
+
+
+def bf16(bits):
+    return torch.from_numpy(bits.astype(np.int16)).view(torch.bfloat16)
+
+
+def run(x, g, W, eps, **kw):
+    y = kb.rmsnorm_linear(x.to(DEV), None if g is None else g.to(DEV), W.to(DEV), eps, **kw)
+    torch.cuda.synchronize()
+    kb.check_status()
+    return y.cpu()
+
+
+def test_library_is_loaded_native():
+    lib = _lib.load()
+    assert lib.rl_version() >= 1000
+    assert os.path.exists(os.path.join(os.path.dirname(kb.__file__), "librmsnorm_linear.so"))
+
+
+@pytest.mark.parametrize("name,has_gamma", [("bf16_outliers_128x256x128.npz", False), ("bf16_gamma_67x136x192.npz", True)])
+def test_golden_vectors(golden_dir, name, has_gamma):
+    g = np.load(os.path.join(golden_dir, name))
+    x, W, eps = bf16(g["x_bits"]), bf16(g["W_bits"]), float(g["eps"])
+    gm = bf16(g["gamma_bits"]) if has_gamma else None
+    ref = torch.from_numpy(g["y_ref_fp64"])
+    assert orc.rel_max_err(run(x, gm, W, eps), ref) <= BF16_TOL
+    # the same vectors through the small-M kernel: first 16 / 64 rows
+    for m in (1, 16, 64):
+        assert orc.rel_max_err(run(x[:m].contiguous(), gm, W, eps), ref[:m]) <= BF16_TOL
+
+
+SHAPES = [(M, N, K) for M in (1, 3, 16, 17, 64, 65, 127, 128, 129, 256)
+          for (N, K) in ((8, 64), (128, 128), (136, 64), (256, 320), (520, 128), (1000, 4096))]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("has_gamma", [False, True])
+def test_small_and_ragged_shapes(M, N, K, has_gamma):
+    x, gm, W = orc.make_inputs(M, N, K, seed=M * 1000 + N + K, gamma=has_gamma)
+    eps = 1e-6 if has_gamma else 1e-5
+    ref = orc.reference_fp32(x, gm, W, eps)
+    y = run(x, gm, W, eps)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert orc.rel_max_err(y, ref) <= BF16_TOL
+
+
+@pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
+                                     "prefill_ss_n128"])
+@pytest.mark.parametrize("has_gamma", [False, True])
+def test_every_prefill_variant(variant, has_gamma):
+    M, N, K = 384, 776, 448
+    x, gm, W = orc.make_inputs(M, N, K, seed=11, gamma=has_gamma)
+    ref = orc.reference_fp32(x, gm, W, 1e-6)
+    assert orc.rel_max_err(run(x, gm, W, 1e-6, variant=variant), ref) <= BF16_TOL
+
+
+def test_reference_outlier_distribution():
+    x, _, W = orc.make_inputs_outliers(512, 1024, 2048, seed=18)
+    ref = orc.reference_fp32(x, None, W, 1e-5, dtype=torch.float64)
+    y = run(x, None, W, 1e-5)
+    assert orc.rel_max_err(y, ref) <= BF16_TOL
+    rmse, max_abs, max_rel = orc.ref_metrics(ref.float(), y.float())
+    # torch's own bf16 path (the reference's "torch" line) has the same order of error
+    y_t = orc.torch_rmsnorm_linear(x, None, W, 1e-5)
+    rmse_t, _, _ = orc.ref_metrics(ref.float(), y_t.float())
+    assert rmse <= 2.0 * rmse_t + 1e-6
+
+
+def test_output_buffer_is_not_overrun():
+    """y is carved out of a larger buffer filled with a sentinel; nothing outside y may change."""
+    for (M, N, K) in [(130, 200, 128), (5, 200, 128), (64, 136, 192)]:
+        x, gm, W = orc.make_inputs(M, N, K, seed=2)
+        big = torch.full((M + 16, N + 56), 7.0, dtype=torch.bfloat16, device=DEV)
+        out = big[8:8 + M, 24:24 + N]
+        kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, out=out)
+        torch.cuda.synchronize()
+        ref = orc.reference_fp32(x, gm, W, 1e-6)
+        assert orc.rel_max_err(out.cpu(), ref) <= BF16_TOL
+        mask = torch.ones_like(big, dtype=torch.bool)
+        mask[8:8 + M, 24:24 + N] = False
+        assert bool((big[mask] == 7.0).all())
+
+
+def test_non_multiple_of_8_columns():
+    x, gm, W = orc.make_inputs(200, 77, 128, seed=4)
+    y = run(x, gm, W, 1e-6)
+    assert y.shape == (200, 77)
+    assert orc.rel_max_err(y, orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+
+
+def test_bad_arguments_raise():
+    x, gm, W = orc.make_inputs(16, 64, 64)
+    x, gm, W = x.to(DEV), gm.to(DEV), W.to(DEV)
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x.float(), gm, W)
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x, gm, W[:, :60].contiguous())
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x.t().contiguous().t(), gm, W)            # not row-major
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x[:, :60].contiguous(), gm[:60].contiguous(), W[:, :60].contiguous())  # K % 8 != 0
+    assert kb.rmsnorm_linear(x[:0], gm, W).shape == (0, 64)
+
+
+def test_deterministic_and_workspace_reuse_across_shapes():
+    """Back-to-back launches of different shapes share one workspace; results repeat bit for bit."""
+    outs = {}
+    for rep in range(2):
+        for (M, N, K) in [(4, 28672, 512), (64, 1000, 4096), (16, 384, 256), (300, 520, 320), (1, 28672, 512)]:
+            x, gm, W = orc.make_inputs(M, N, K, seed=9)
+            y = run(x, gm, W, 1e-6)
+            if rep == 0:
+                outs[(M, N, K)] = y
+                assert orc.rel_max_err(y, orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+            else:
+                assert torch.equal(y, outs[(M, N, K)])
+
+
+# ---------------------------------------------------------------- benchmark configurations
+def _sample_check(x, gm, W, y, eps, rows, tol=BF16_TOL):
+    ref = orc.reference_fp32(x[rows], gm, W, eps)
+    return orc.rel_max_err(y[rows], ref)
+
+
+def test_config2_prefill_qkv():
+    M, N, K = 4096, 6144, 4096
+    x, gm, W = orc.make_inputs(M, N, K, seed=18)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    torch.cuda.synchronize()
+    kb.check_status()
+    # full tensor against torch fp32 on the GPU (TF32 off), a row sample against the CPU oracle
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref_gpu = orc.reference_fp32(xd, gd, Wd, 1e-6)
+    assert orc.rel_max_err(y, ref_gpu) <= BF16_TOL
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(0))[:48]
+    assert _sample_check(x, gm, W, y.cpu(), 1e-6, rows) <= BF16_TOL
+    # size-independent properties
+    y2 = kb.rmsnorm_linear(xd * 4, gd, Wd, 1e-6)                      # rms_norm is scale-invariant (eps aside)
+    assert orc.rel_max_err(y2, y.float()) <= 2e-3
+    n0, n1 = 1536, 3072                                               # a column shard reproduces its columns exactly
+    ys = kb.rmsnorm_linear(xd, gd, Wd[n0:n1], 1e-6)
+    assert torch.equal(ys, y[:, n0:n1])
+    assert torch.equal(kb.rmsnorm_linear(xd, gd, Wd, 1e-6), y)        # run-to-run identical
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 64])
+def test_config3_decode(M):
+    N, K = 28672, 4096
+    x, gm, W = orc.make_inputs(M, N, K, seed=18 + M)
+    y = run(x, gm, W, 1e-6)
+    ref = orc.reference_fp32(x, gm, W, 1e-6)
+    assert orc.rel_max_err(y, ref) <= BF16_TOL
+    assert torch.equal(run(x, gm, W, 1e-6), y)
+    # the same rows through the large-M kernel agree to bf16 rounding
+    xp = torch.zeros(128, K, dtype=torch.bfloat16)
+    xp[:M] = x
+    yp = run(xp, gm, W, 1e-6, variant="prefill_ts_n192")[:M]
+    assert orc.rel_max_err(yp, y.float()) <= 1e-2
+
+
+def test_config4_one_of_eight_shards():
+    """16384 x 57344 x 8192 split over 8 ranks: rank 3's shard (7168 channels) at full M and K."""
+    M, N, K, G, r = 16384, 57344, 8192, 8, 3
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    gm = (1 + 0.1 * torch.randn(K, generator=g)).bfloat16()
+    Wl = (torch.randn(N // G, K, generator=g) * K ** -0.5).bfloat16()
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), Wl.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    worst = 0.0
+    for m0 in range(0, M, 4096):
+        ref = orc.reference_fp32(xd[m0:m0 + 4096], gd, Wd, 1e-6)
+        worst = max(worst, orc.rel_max_err(y[m0:m0 + 4096], ref))
+    assert worst <= BF16_TOL
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(r))[:16]
+    assert _sample_check(x, gm, Wl, y.cpu(), 1e-6, rows) <= BF16_TOL

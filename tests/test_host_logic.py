@@ -1,0 +1,98 @@
+"""Host-side logic that needs no GPU: argument checks of the Python operator, shard arithmetic,
+and the column-parallel gather run as two gloo ranks on the CPU with the oracle standing in for
+the device kernel."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import kernel_benchmarking_b200 as kb
+from kernel_benchmarking_b200.sharding import ColumnParallelRMSNormLinear, shard_bounds, shard_rows
+from oracle import rmsnorm_linear_oracle as orc
+
+
+def test_operator_rejects_cpu_tensors_and_bad_shapes():
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    W = torch.zeros(8, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        kb.rmsnorm_linear(x, None, W, 1e-6)   # no CPU path: must refuse, not fall back
+    with pytest.raises(TypeError):
+        kb.rmsnorm_linear([1, 2], None, W)
+
+
+@pytest.mark.parametrize("N,world", [(57344, 1), (57344, 2), (57344, 4), (57344, 8), (14336, 8), (1000, 3), (8, 4), (7, 2)])
+def test_shard_bounds_partition(N, world):
+    prev = 0
+    sizes = []
+    for r in range(world):
+        a, b = shard_bounds(N, world, r)
+        assert a == prev and b >= a
+        if r < world - 1:
+            assert a % 8 == 0 and b % 8 == 0
+        prev = b
+        sizes.append(b - a)
+    assert prev == N
+    if N % (8 * world) == 0:
+        assert len(set(sizes)) == 1 and sizes[0] == N // world
+
+
+def test_shard_bounds_config_sizes():
+    assert [shard_bounds(57344, g, 0)[1] for g in (1, 2, 4, 8)] == [57344, 28672, 14336, 7168]
+    assert shard_bounds(14336, 8, 7) == (12544, 14336)
+    with pytest.raises(ValueError):
+        shard_bounds(8, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, N, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, K = 24, 128
+        x, gm, W = orc.make_inputs(M, N, K, seed=5, dtype=torch.float32)
+
+        def cpu_stand_in(x_, g_, W_, eps):
+            return orc.torch_rmsnorm_linear(x_, g_, W_, eps)
+
+        op = ColumnParallelRMSNormLinear(shard_rows(W, world, rank), gm, 1e-6, N, local_fn=cpu_stand_in)
+        y_local = op.forward(x)
+        n0, n1 = shard_bounds(N, world, rank)
+        full = orc.torch_rmsnorm_linear(x, gm, W, 1e-6)
+        ok_local = torch.allclose(y_local, full[:, n0:n1], rtol=1e-5, atol=1e-6)
+        y = op.gather(y_local)
+        ok_full = y.shape == full.shape and torch.allclose(y, full, rtol=1e-5, atol=1e-6)
+        q.put((rank, bool(ok_local), bool(ok_full)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N", [64, 72])   # equal blocks (all_gather_into_tensor) and ragged blocks
+def test_column_parallel_gather_two_gloo_ranks(N):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, N, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    res = sorted(q.get(timeout=10) for _ in procs)
+    assert res == [(0, True, True), (1, True, True)]
+
+
+def test_wrong_shard_size_is_rejected():
+    W = torch.zeros(10, 16)
+    with pytest.raises(ValueError, match="rows of W"):
+        ColumnParallelRMSNormLinear(W, None, 1e-6, 64, local_fn=lambda *a: None)
