@@ -199,6 +199,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--variant", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="only warm-up + timed steps (no clock-sampling spin, no e2e, no CPU baseline): for ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -245,7 +247,7 @@ def main():
     # keep the GPU busy long enough for nvidia-smi to sample it under load, then time exactly K steps
     t_spin = time.perf_counter()
     i = 0
-    while time.perf_counter() - t_spin < 0.3:
+    while not args.profile and time.perf_counter() - t_spin < 0.3:
         step(i)
         i += 1
         if i % 16 == 0:
@@ -270,6 +272,14 @@ def main():
         value, unit = world * flops / (ms_step * 1e-3) / 1e12, "TFLOP/s"
     else:
         value, unit = world * step_bytes / (ms_step * 1e-3) / 1e9, "GB/s"
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": args.workload, "ms_per_step": ms_step, "value": value,
+                              "unit": unit}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---------------- end to end: host buffers, copies inside the timed region
     x_host = [b[4].pin_memory() for b in bufs[:2]]

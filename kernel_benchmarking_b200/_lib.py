@@ -32,6 +32,7 @@ VARIANTS = {
     "prefill_ss_n256": 3,
     "prefill_ts_n128": 4,
     "prefill_ss_n128": 5,
+    "x6": 6, "x7": 7, "x8": 8,
     "decode": 20,
 }
 

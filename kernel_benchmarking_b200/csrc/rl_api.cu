@@ -216,20 +216,23 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
 
   if (decode) {
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-    if (M <= 16) return launch_decode<DecodeCfg<16, 10>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
-    if (M <= 32) return launch_decode<DecodeCfg<32, 9>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+    if (M <= 16) return launch_decode<DecodeCfg<16, 12>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+    if (M <= 32) return launch_decode<DecodeCfg<32, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
     return launch_decode<DecodeCfg<64, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
   }
 
   if (variant == RL_VARIANT_AUTO) variant = RL_VARIANT_PREFILL_TS_N192;
-#define RL_PREFILL(BN, ST, AM) \
-  launch_prefill<PrefillCfg<BN, ST, AM>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
+#define RL_PREFILL(BN, ST, AM, TG) \
+  launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
   switch (variant) {
-    case RL_VARIANT_PREFILL_TS_N192: return RL_PREFILL(192, 4, A_TS_FOLD);
-    case RL_VARIANT_PREFILL_SS_N192: return g ? RL_PREFILL(192, 4, A_SS_FOLD) : RL_PREFILL(192, 4, A_SS_DIRECT);
-    case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD) : RL_PREFILL(256, 4, A_SS_DIRECT);
-    case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 6, A_TS_FOLD);
-    case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 6, A_SS_FOLD) : RL_PREFILL(128, 6, A_SS_DIRECT);
+    case RL_VARIANT_PREFILL_TS_N192: return RL_PREFILL(192, 4, A_TS_FOLD, 2);
+    case RL_VARIANT_PREFILL_SS_N192: return g ? RL_PREFILL(192, 4, A_SS_FOLD, 2) : RL_PREFILL(192, 4, A_SS_DIRECT, 2);
+    case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD, 1) : RL_PREFILL(256, 4, A_SS_DIRECT, 1);
+    case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 4, A_TS_FOLD, 2);
+    case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 4, A_SS_FOLD, 2) : RL_PREFILL(128, 4, A_SS_DIRECT, 2);
+    case 6: return RL_PREFILL(192, 3, A_TS_FOLD, 1);
+    case 7: return RL_PREFILL(192, 2, A_TS_FOLD, 1);
+    case 8: return RL_PREFILL(192, 4, A_TS_FOLD, 1);
     default: return RL_ERR_BAD_VARIANT;
   }
 #undef RL_PREFILL

@@ -43,14 +43,18 @@ struct DecodeCfg {
   static constexpr int OFF_X = OFF_W + STAGES * W_BYTES;
   static constexpr int OFF_G = OFF_X + STAGES * X_BYTES;
   static constexpr int OFF_SSQ = OFF_G + STAGES * G_BYTES;
-  static constexpr int OFF_BAR = OFF_SSQ + 2 * MPAD * 4;
+  static constexpr int OFF_RVEC = OFF_SSQ + 4 * 2 * MPAD * 4;
+  static constexpr int OFF_BAR = OFF_RVEC + MPAD * 4;
   static constexpr int NUM_BARS = 3 * STAGES + 6;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
   static constexpr int TMEM_COLS = (2 * MPAD < 32) ? 32 : 2 * MPAD;
-  static constexpr int NCH = MPAD / 16;  // 16-byte chunks of the x tile per transform thread
+  static constexpr int NCH = MPAD / 4;  // 16-byte chunks of the x tile per lane of the warp that transforms a unit
   static_assert(MPAD == 16 || MPAD == 32 || MPAD == 64, "MPAD");
   static_assert(X_BYTES % 1024 == 0, "x stage alignment");
+  // units are dealt to the 4 transform warps round-robin; a ring slot must always belong to the same
+  // warp, or a warp that skipped a slot's previous phase could mistake it for its own (parity aliasing)
+  static_assert(STAGES % 4 == 0, "STAGES must be a multiple of 4");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -84,7 +88,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
   volatile int* epi_last = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 12);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
-  float* ssq = reinterpret_cast<float*>(smem + Cfg::OFF_SSQ);  // [2][MPAD]
+  float* ssq = reinterpret_cast<float*>(smem + Cfg::OFF_SSQ);    // [4 warps][2][MPAD] partial sums of squares
+  float* rvec = reinterpret_cast<float*>(smem + Cfg::OFF_RVEC);  // [MPAD] 1/rms per token of the tile being finished
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = p.KB;
@@ -96,7 +101,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_xf(s), 4);
+      mbar_init(bar_xf(s), 1);
       mbar_init(bar_empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -174,10 +179,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------------------------------------ transform
-    const int tt = threadIdx.x - 64;  // 0..127
-    const int c = tt & 7;             // 16-byte chunk within the 128-byte row
-    int s = 0;
-    uint32_t ph = 0;
+    // The x tile of one unit is small (MPAD x 128 bytes), so one warp handles a whole unit and
+    // the four warps take units round-robin: four units are in flight in this role at once.
+    const int tw = warp - 2;     // 0..3
+    const int c = lane & 7;      // 16-byte chunk within the 128-byte row
     bool ok = true;
     int seg = 0;
     for (int u = u_begin; ok && u < u_end; ++seg) {
@@ -188,7 +193,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       float ss[NCH];
 #pragma unroll
       for (int i = 0; i < NCH; ++i) ss[i] = 0.f;
-      for (int i = 0; i < n_units; ++i) {
+      const int j0 = u - u_begin;  // running unit index of the CTA = ring position
+      for (int i = ((tw - j0) % 4 + 4) % 4; i < n_units; i += 4) {
+        const int j = j0 + i;
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
         ok = mbar_wait(bar_full(s), ph, ctl, 2, s, u + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -198,16 +207,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const bool cvalid = (c * 8 < kvalid);
         if (has_gamma && cvalid) gv = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES)[c];
 #pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-          const int row = (tt >> 3) + j * 16;
+        for (int jj = 0; jj < NCH; ++jj) {
+          const int row = (lane >> 3) + jj * 4;
           uint4* ptr = reinterpret_cast<uint4*>(xt + row * 128 + ((c ^ (row & 7)) << 4));
           uint4 v = *ptr;
-          float a = ss[j];
+          float a = ss[jj];
           a = fmaf(bf16lo(v.x), bf16lo(v.x), a); a = fmaf(bf16hi(v.x), bf16hi(v.x), a);
           a = fmaf(bf16lo(v.y), bf16lo(v.y), a); a = fmaf(bf16hi(v.y), bf16hi(v.y), a);
           a = fmaf(bf16lo(v.z), bf16lo(v.z), a); a = fmaf(bf16hi(v.z), bf16hi(v.z), a);
           a = fmaf(bf16lo(v.w), bf16lo(v.w), a); a = fmaf(bf16hi(v.w), bf16hi(v.w), a);
-          ss[j] = a;
+          ss[jj] = a;
           if (has_gamma) {
             if (cvalid) {
               v.x = mul_bf16x2(v.x, gv.x); v.y = mul_bf16x2(v.y, gv.y);
@@ -221,24 +230,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         if (has_gamma) fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_xf(s));
-        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (!ok) break;
       // each token row is spread over 8 neighbouring lanes: butterfly-reduce
 #pragma unroll
-      for (int j = 0; j < NCH; ++j) {
-        float a = ss[j];
+      for (int jj = 0; jj < NCH; ++jj) {
+        float a = ss[jj];
         a += __shfl_xor_sync(0xffffffffu, a, 1);
         a += __shfl_xor_sync(0xffffffffu, a, 2);
         a += __shfl_xor_sync(0xffffffffu, a, 4);
-        ss[j] = a;
+        ss[jj] = a;
       }
       ok = mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 2, 3 * STAGES + 2 + acc, seg);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (c == 0) {
 #pragma unroll
-        for (int j = 0; j < NCH; ++j) ssq[acc * MPAD + (tt >> 3) + j * 16] = ss[j];
+        for (int jj = 0; jj < NCH; ++jj) ssq[(tw * 2 + acc) * MPAD + (lane >> 3) + jj * 4] = ss[jj];
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_rs(acc));
@@ -276,18 +284,27 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       }
       const int n = tile * 128 + n_local;
       const bool whole = (n_units == KB);
+      // one thread per token adds up the four transform warps' shares of the sum of squares
+      float tot = 0.f;
+      if (epi_tid < MPAD) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) tot += ssq[(w * 2 + acc) * MPAD + epi_tid];
+      }
       bool finish = whole;
-      if (!whole) {
+      if (whole) {
+        if (epi_tid < MPAD) rvec[epi_tid] = 1.0f / sqrtf(tot * inv_k + p.eps);
+        named_bar_sync(1, 128);
+      } else {
         const int slot = (seg == 0) ? 0 : 1;
         float* part = p.partials + (size_t)(cta * 2 + slot) * MPAD * 128;
 #pragma unroll
         for (int m = 0; m < MPAD; ++m) part[m * 128 + n_local] = a[m];
-        if (epi_tid < MPAD) p.ssq_partials[(cta * 2 + slot) * MPAD + epi_tid] = ssq[acc * MPAD + epi_tid];
+        if (epi_tid < MPAD) p.ssq_partials[(cta * 2 + slot) * MPAD + epi_tid] = tot;
         __threadfence();
         named_bar_sync(1, 128);
+        const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
+        const int last = sk_cta_of_unit(tile * KB + KB - 1, p.units_total, G);
         if (epi_tid == 0) {
-          const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
-          const int last = sk_cta_of_unit(tile * KB + KB - 1, p.units_total, G);
           const int old = atomicAdd(p.counters + tile, 1);
           const int is_last = (old == last - first);
           if (is_last) p.counters[tile] = 0;  // ready for the next launch
@@ -296,39 +313,30 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         }
         named_bar_sync(2, 128);
         finish = (*epi_last != 0);
-      }
-      if (finish) {
-        if (!whole) {
-          const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
-          const int last = sk_cta_of_unit(tile * KB + KB - 1, p.units_total, G);
+        if (finish) {
+          // last to arrive: add the contributors' partial tiles in contributor order
 #pragma unroll
           for (int m = 0; m < MPAD; ++m) a[m] = 0.f;
+          float s2 = 0.f;
           for (int cc = first; cc <= last; ++cc) {
             const int cslot = (sk_begin(cc, p.units_total, G) / KB == tile) ? 0 : 1;
-            const float* part = p.partials + (size_t)(cc * 2 + cslot) * MPAD * 128;
+            const float* cpart = p.partials + (size_t)(cc * 2 + cslot) * MPAD * 128;
+            float ld[MPAD];
 #pragma unroll
-            for (int m = 0; m < MPAD; ++m) a[m] += __ldcg(part + m * 128 + n_local);
-          }
+            for (int m = 0; m < MPAD; ++m) ld[m] = __ldcg(cpart + m * 128 + n_local);
+            if (epi_tid < MPAD) s2 += __ldcg(p.ssq_partials + (cc * 2 + cslot) * MPAD + epi_tid);
 #pragma unroll
-          for (int m = 0; m < MPAD; ++m) {
-            if (m < p.M) {
-              float s2 = 0.f;
-              for (int cc = first; cc <= last; ++cc) {
-                const int cslot = (sk_begin(cc, p.units_total, G) / KB == tile) ? 0 : 1;
-                s2 += __ldcg(p.ssq_partials + (cc * 2 + cslot) * MPAD + m);
-              }
-              const float r = 1.0f / sqrtf(s2 * inv_k + p.eps);
-              if (n < p.N) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * r);
-            }
+            for (int m = 0; m < MPAD; ++m) a[m] += ld[m];
           }
-        } else {
+          if (epi_tid < MPAD) rvec[epi_tid] = 1.0f / sqrtf(s2 * inv_k + p.eps);
+          named_bar_sync(5, 128);
+        }
+      }
+      if (finish) {
+        if (n < p.N) {
 #pragma unroll
-          for (int m = 0; m < MPAD; ++m) {
-            if (m < p.M) {
-              const float r = 1.0f / sqrtf(ssq[acc * MPAD + m] * inv_k + p.eps);
-              if (n < p.N) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * r);
-            }
-          }
+          for (int m = 0; m < MPAD; ++m)
+            if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * rvec[m]);
         }
       }
       // accumulator and ssq[acc] fully consumed

@@ -5,11 +5,11 @@
 // One persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
 //   warp 0      TMA producer: x tile [128 x 64], W tile [BN x 64], gamma slice, per k-block
 //   warp 1      UMMA issuer (tcgen05.mma, fp32 accumulators in TMEM, two buffers)
-//   warps 2-5   transform: each thread owns one token row of the landed x tile,
+//   TG x 4 warps transform (k-blocks dealt round-robin to TG groups): each thread owns one token row of the landed x tile,
 //               accumulates its sum of squares in fp32 and folds gamma into the
 //               tile - back into shared memory (A_SS_FOLD) or into tensor memory
 //               as the UMMA A operand (A_TS_FOLD)
-//   warps 6-9   epilogue: tcgen05.ld, multiply each row by its 1/rms, bf16,
+//   last 4 warps epilogue: tcgen05.ld, multiply each row by its 1/rms, bf16,
 //               swizzled staging tile, TMA store
 // The reference's fused kernels use the same algebra - accumulate x@W^T and
 // sum(x^2) together, scale in the epilogue (python/bench_kernels/helion/
@@ -29,10 +29,11 @@ struct PrefillParams {
   int* status;  // RL_STATUS_INTS ints or nullptr
 };
 
-template <int BN_, int STAGES_, int AMODE_>
+template <int BN_, int STAGES_, int AMODE_, int TG_ = 2>
 struct PrefillCfg {
   static constexpr int BM = 128, BK = 64, BN = BN_, STAGES = STAGES_, AMODE = AMODE_;
-  static constexpr int THREADS = 320;
+  static constexpr int TG = TG_;                       // transform groups of 4 warps; group g takes k-blocks j = g (mod TG)
+  static constexpr int THREADS = 64 + 128 * TG + 128;  // producer, MMA, TG x 4 transform warps, 4 epilogue warps
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int G_BYTES = BK * 2;
@@ -42,13 +43,16 @@ struct PrefillCfg {
   static constexpr int OFF_EPI = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_G = OFF_EPI + 2 * EPI_BYTES;
   static constexpr int OFF_RS = OFF_G + STAGES * G_BYTES;
-  static constexpr int OFF_BAR = OFF_RS + 2 * 128 * 4;
+  static constexpr int OFF_BAR = OFF_RS + TG * 2 * 128 * 4;
   static constexpr int NUM_BARS = 3 * STAGES + 6;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;  // + alignment slack
   static constexpr int TMEM_COLS = 512;
   static constexpr int A_COL0 = 2 * BN;  // TMEM columns of the A stages (A_TS_FOLD)
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN");
+  // A ring slot must always be served by the same transform group: a group that skipped a slot's
+  // previous phase could mistake that phase for the one it is waiting for (parity waits alias).
+  static_assert(STAGES % TG == 0, "STAGES must be a multiple of TG");
   static_assert(AMODE != A_TS_FOLD || 2 * BN + STAGES * 32 <= 512, "TMEM budget");
   static_assert(2 * BN <= 512, "TMEM budget");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -101,7 +105,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull(a), 1);
       mbar_init(bar_tempty(a), 4);
-      mbar_init(bar_rs(a), 4);
+      mbar_init(bar_rs(a), 4 * Cfg::TG);
     }
     ctl->abort = 0;
     ctl->status = p.status;
@@ -182,20 +186,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 2 + 4 * Cfg::TG) {
     // ------------------------------------------------------------ transform: sum of squares + gamma fold
+    constexpr int TG = Cfg::TG;
+    const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t swz = (uint32_t)(row & 7);
-    int s = 0;
-    uint32_t ph = 0;
     bool ok = true;
     int it = 0;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+    int j_base = 0;  // index of this tile's first k-block in the CTA's running count (ring slot = j % STAGES)
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it, j_base += KB) {
       const int acc = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       float ss = 0.f;
-      for (int kb = 0; kb < KB; ++kb) {
+      for (int kb = (grp - j_base % TG + TG) % TG; kb < KB; kb += TG) {
+        const int j = j_base + kb;
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
         ok = mbar_wait(bar_full(s), ph, ctl, 2, s, kb);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -208,8 +216,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         }
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float lo = bf16lo(v[j]), hi = bf16hi(v[j]);
+        for (int jj = 0; jj < 32; ++jj) {
+          const float lo = bf16lo(v[jj]), hi = bf16hi(v[jj]);
           s0 = fmaf(lo, lo, s0);
           s1 = fmaf(hi, hi, s1);
         }
@@ -248,14 +256,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_xf(s));
-        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (!ok) break;
-      // rs[acc] was last read by the epilogue of the tile two iterations back
+      // rs[.][acc] was last read by the epilogue of the tile two iterations back
       ok = mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 2, 3 * STAGES + 2 + acc, it);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      rs[acc * 128 + row] = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+      rs[(grp * 2 + acc) * 128 + row] = ss;  // this group's share of the row's sum of squares
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_rs(acc));
     }
@@ -264,7 +271,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t swz = (uint32_t)(row & 7);
-    const int epi_tid = threadIdx.x - 192;
+    const int epi_tid = threadIdx.x - (64 + 128 * Cfg::TG);
     bool ok = true;
     int it = 0;
     uint32_t chunk_no = 0;
@@ -283,7 +290,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       ok = (*epi_go != 0);
       if (!ok) break;
       tc_fence_after();
-      const float r = rs[acc * 128 + row];
+      float ssum = 0.f;
+#pragma unroll
+      for (int g = 0; g < Cfg::TG; ++g) ssum += rs[(g * 2 + acc) * 128 + row];
+      const float r = 1.0f / sqrtf(ssum / (float)p.K + p.eps);
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c, ++chunk_no) {
         uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;

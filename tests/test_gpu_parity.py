@@ -155,7 +155,7 @@ def test_config2_prefill_qkv():
     assert _sample_check(x, gm, W, y.cpu(), 1e-6, rows) <= BF16_TOL
     # size-independent properties
     y2 = kb.rmsnorm_linear(xd * 4, gd, Wd, 1e-6)                      # rms_norm is scale-invariant (eps aside)
-    assert orc.rel_max_err(y2, y.float()) <= 2e-3
+    assert orc.rel_max_err(y2, y.float()) <= 5e-3                     # one bf16 ulp at max|y| is 3.9e-3
     n0, n1 = 1536, 3072                                               # a column shard reproduces its columns exactly
     ys = kb.rmsnorm_linear(xd, gd, Wd[n0:n1], 1e-6)
     assert torch.equal(ys, y[:, n0:n1])
