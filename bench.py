@@ -197,7 +197,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--variant", default="auto")
+    ap.add_argument("--variant", default="auto", help="kernel variant name (see kernel_benchmarking_b200._lib.VARIANTS)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + timed steps (no clock-sampling spin, no e2e, no CPU baseline): for ncu")

@@ -32,6 +32,10 @@ VARIANTS = {
     "prefill_ss_n256": 3,
     "prefill_ts_n128": 4,
     "prefill_ss_n128": 5,
+    "prefill_pair_n256": 9,
+    "prefill_pair_n192": 10,
+    "prefill_pair_direct": 11,
+    "x12": 12, "x13": 13,
     "x6": 6, "x7": 7, "x8": 8,
     "decode": 20,
 }

@@ -2,10 +2,12 @@
 // Declarations and the reference interfaces they replace: include/rmsnorm_linear.h
 #include "../../include/rmsnorm_linear.h"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "rl_decode.cuh"
 #include "rl_prefill.cuh"
+#include "rl_prefill_pair.cuh"
 
 namespace {
 
@@ -122,6 +124,57 @@ int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, voi
 }
 
 template <class Cfg>
+int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
+                        int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st) {
+  CUtensorMap tx, tw, ty;
+  int rc;
+  if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
+  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, N, ldw, 64, Cfg::BN / 2))) return rc;
+  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
+  if (Cfg::AMODE == A_SS_DIRECT && gamma != nullptr) return RL_ERR_BAD_VARIANT;
+  PrefillParams p{};
+  p.M = M; p.N = N; p.K = K; p.eps = eps;
+  p.gamma = gamma;
+  p.m_tiles = (M + 255) / 256;
+  p.n_tiles = (N + Cfg::BN - 1) / Cfg::BN;
+  p.group_m = 8;
+  p.status = status;
+#ifdef RL_TRACE
+  p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
+  p.trace = status ? reinterpret_cast<long long*>(reinterpret_cast<uint8_t*>(status) + 4096) : nullptr;
+#endif
+  cudaError_t e = cudaFuncSetAttribute(prefill_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_err(e);
+  // how many CTA pairs the device can hold at once (pairs must sit on neighbouring SMs)
+  static int max_pairs_cache[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int max_pairs = max_pairs_cache[dev & 63];
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sms / 2));
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, prefill_pair_kernel<Cfg>, &cfg);
+    if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / 2; }
+    max_pairs = n;
+    max_pairs_cache[dev & 63] = n;
+  }
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
+template <class Cfg>
 int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                   int64_t ldx, int64_t ldw, int64_t ldy, float eps, uint8_t* ws, const WsLayout& wl, int sms,
                   cudaStream_t st) {
@@ -221,7 +274,8 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     return launch_decode<DecodeCfg<64, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
   }
 
-  if (variant == RL_VARIANT_AUTO) variant = RL_VARIANT_PREFILL_TS_N192;
+  // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
+  if (variant == RL_VARIANT_AUTO) variant = (M > 128) ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_TS_N192;
 #define RL_PREFILL(BN, ST, AM, TG) \
   launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
   switch (variant) {
@@ -230,6 +284,14 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD, 1) : RL_PREFILL(256, 4, A_SS_DIRECT, 1);
     case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 4, A_TS_FOLD, 2);
     case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 4, A_SS_FOLD, 2) : RL_PREFILL(128, 4, A_SS_DIRECT, 2);
+#define RL_PAIR(BN, NACC, ST, AS, TG, AM) \
+  launch_prefill_pair<PairCfg<BN, NACC, ST, AS, TG, AM>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
+    case RL_VARIANT_PREFILL_PAIR_N256: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD);
+    case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
+    case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
+    case 12: return RL_PAIR(192, 2, 6, 3, 3, A_TS_FOLD);
+    case 13: return RL_PAIR(256, 1, 6, 6, 3, A_TS_FOLD);
+#undef RL_PAIR
     case 6: return RL_PREFILL(192, 3, A_TS_FOLD, 1);
     case 7: return RL_PREFILL(192, 2, A_TS_FOLD, 1);
     case 8: return RL_PREFILL(192, 4, A_TS_FOLD, 1);

@@ -126,28 +126,30 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    {
       const uint64_t pol_w = l2_policy_evict_first();  // W is streamed exactly once
       const uint64_t pol_x = l2_policy_evict_last();   // x is re-read by every CTA
       int s = 0;
       uint32_t ph = 0;
       int tile = u_begin / KB, kb = u_begin - tile * KB;
       for (int u = u_begin; u < u_end; ++u) {
-        if (!mbar_wait(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, u)) break;
-        const int kvalid = min(64, p.K - kb * 64);
-        const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
-        mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
-        tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
-        tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
-        if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+        if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, u)) break;
+        if (elect_one()) {
+          const int kvalid = min(64, p.K - kb * 64);
+          const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
+          mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
+          tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
+          tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
+          if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+        }
+        __syncwarp();
         if (++s == STAGES) { s = 0; ph ^= 1; }
         if (++kb == KB) { kb = 0; ++tile; }
       }
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc(128, MPAD, 1, 1);
       int s = 0;
       uint32_t ph = 0;
@@ -158,25 +160,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const int n_units = min(KB - kb0, u_end - u);
         const int acc = seg & 1;
         const uint32_t aph = (seg >> 1) & 1;
-        if (!mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, seg)) break;
+        if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, seg)) break;
         tc_fence_after();
         const uint32_t d = tmem_base + acc * MPAD;
         for (int i = 0; i < n_units; ++i) {
-          if (!mbar_wait(bar_full(s), ph, ctl, 1, s, u + i)) { ok = false; break; }
-          if (!mbar_wait(bar_xf(s), ph, ctl, 1, STAGES + s, u + i)) { ok = false; break; }
+          if (!mbar_wait_warp(bar_full(s), ph, ctl, 1, s, u + i)) { ok = false; break; }
+          if (!mbar_wait_warp(bar_xf(s), ph, ctl, 1, STAGES + s, u + i)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_W + s * Cfg::W_BYTES);
           const uint64_t bdesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_X + s * Cfg::X_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
-          umma_commit(bar_empty(s));
+            for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+            umma_commit(bar_empty(s));
+          }
+          __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(bar_tfull(acc));
+        if (ok && elect_one()) umma_commit(bar_tfull(acc));
+        __syncwarp();
         u += n_units;
       }
     }
-    __syncwarp();
   } else if (warp < 6) {
     // ------------------------------------------------------------ transform
     // The x tile of one unit is small (MPAD x 128 bytes), so one warp handles a whole unit and

@@ -27,6 +27,8 @@ struct PrefillParams {
   const __nv_bfloat16* gamma;  // [K] or nullptr (only with A_SS_DIRECT / treated as ones)
   int m_tiles, n_tiles, group_m;
   int* status;  // RL_STATUS_INTS ints or nullptr
+  long long* trace;  // timeline stamps of CTA pair 0 (only read by builds with RL_TRACE)
+  int debug;         // experiment switches, honoured only by builds with RL_TRACE (results become wrong)
 };
 
 template <int BN_, int STAGES_, int AMODE_, int TG_ = 2>
@@ -125,7 +127,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -133,21 +135,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         int mt, nt;
         prefill_tile_coords(t, p, mt, nt);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
-          const int kvalid = min(64, p.K - kb * 64);
-          const uint32_t gbytes = (has_gamma && AMODE != A_SS_DIRECT) ? (uint32_t)kvalid * 2u : 0u;
-          mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES + gbytes);
-          tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, &tm_x, bar_full(s), kb * 64, mt * 128);
-          tma_load_2d(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, bar_full(s), kb * 64, nt * BN);
-          if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+          if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
+          if (elect_one()) {
+            const int kvalid = min(64, p.K - kb * 64);
+            const uint32_t gbytes = (has_gamma && AMODE != A_SS_DIRECT) ? (uint32_t)kvalid * 2u : 0u;
+            mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES + gbytes);
+            tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, &tm_x, bar_full(s), kb * 64, mt * 128);
+            tma_load_2d(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, bar_full(s), kb * 64, nt * BN);
+            if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+          }
+          __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc(128, BN, 1, 1);
       int s = 0;
       uint32_t ph = 0;
@@ -156,36 +160,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t aph = (it >> 1) & 1;
-        if (!mbar_wait(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, it)) break;
+        if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, it)) break;
         tc_fence_after();
         const uint32_t d = tmem_base + acc * BN;
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(bar_full(s), ph, ctl, 1, s, kb)) { ok = false; break; }
+          if (!mbar_wait_warp(bar_full(s), ph, ctl, 1, s, kb)) { ok = false; break; }
           if (AMODE != A_SS_DIRECT) {
-            if (!mbar_wait(bar_xf(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
+            if (!mbar_wait_warp(bar_xf(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
           }
           tc_fence_after();
           const uint64_t bdesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_B + s * Cfg::B_BYTES);
-          if (AMODE == A_TS_FOLD) {
-            const uint32_t a_t = tmem_base + Cfg::A_COL0 + s * 32;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_ts(d, a_t + k * 8, bdesc + 2 * k, idesc, (kb | k) != 0);
-          } else {
-            const uint64_t adesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_A + s * Cfg::A_BYTES);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-          }
+          const uint64_t adesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_A + s * Cfg::A_BYTES);
+          const uint32_t a_t = tmem_base + Cfg::A_COL0 + s * 32;
           if (AMODE == A_SS_DIRECT) {
+            if (elect_one()) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            }
+            __syncwarp();
             // the row-statistics warps must be done reading the x tile before its slot is recycled
-            if (!mbar_wait(bar_xf(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
+            if (!mbar_wait_warp(bar_xf(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
+            if (elect_one()) umma_commit(bar_empty(s));
+          } else if (elect_one()) {
+            if (AMODE == A_TS_FOLD) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_ts(d, a_t + k * 8, bdesc + 2 * k, idesc, (kb | k) != 0);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            }
+            umma_commit(bar_empty(s));
           }
-          umma_commit(bar_empty(s));
+          __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(bar_tfull(acc));
+        if (ok && elect_one()) umma_commit(bar_tfull(acc));
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else if (warp < 2 + 4 * Cfg::TG) {
     // ------------------------------------------------------------ transform: sum of squares + gamma fold
     constexpr int TG = Cfg::TG;

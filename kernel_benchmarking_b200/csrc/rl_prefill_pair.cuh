@@ -1,0 +1,386 @@
+// Fused RMSNorm -> Linear for large M on CTA pairs (cluster of 2, tcgen05 cta_group::2).
+//
+// A pair of CTAs on neighbouring SMs computes one 256 x BN output tile.  Each CTA loads only
+// its own halves - x rows [128 x 64] and W rows [BN/2 x 64] per k-block, no multicast - and
+// the pair's MMA (M = 256, N = BN, issued by one lane of the rank-0 CTA) reads both W halves
+// from the two CTAs' shared memory, so every byte brought in from L2 feeds twice the math of
+// a single-CTA tile.
+//
+// A_TS_FOLD: the gamma-folded activation tile is the MMA's A operand in tensor memory.  The
+//   transform warps read the landed x tile from shared memory, accumulate each row's sum of
+//   squares, multiply by gamma and tcgen05.st the result into a ring of ASLOTS A slots that
+//   sits behind the accumulators.
+// A_SS_DIRECT (gamma == nullptr, the reference operator): the MMA reads x straight from
+//   shared memory; the transform warps only accumulate the sums of squares.
+// TMEM per CTA: NACC accumulators of BN columns, then ASLOTS x 32 columns of A ring.
+//
+// Barriers (shared memory, identical offsets in both CTAs):
+//   fullA[s]    local        x tile + gamma slice landed              producer -> own transform warps
+//   ready[s]    rank 0 only  both W halves landed (2 arrivals + tx) and both CTAs' transform warps
+//                            done with slot s (8 arrivals): the one wait per k-block of the MMA loop
+//   empty[s]    local        MMAs that read slot s are done            MMA commit (multicast) -> producers,
+//                                                                      and -> transform warps (A slot reuse)
+//   tfull[a]    local        accumulator a complete                    MMA commit (multicast) -> epilogues
+//   tempty[a]   rank 0 only  both epilogues drained accumulator a (8 arrivals) -> MMA warp
+//   rsfull[a]   local        row sums of squares written               transform -> own epilogue
+//   rsfree[a]   local        row sums consumed                         epilogue -> own transform warps
+#pragma once
+#include "rl_prefill.cuh"
+
+namespace rl {
+
+// Optional timeline instrumentation (compile with -DRL_TRACE): clock64 stamps of the first
+// RL_TRACE_N k-blocks of CTA pair 0, laid out [rank][event][index]; RL_DEBUG switches turn
+// parts of the kernel off for experiments (results become wrong).
+#ifdef RL_TRACE
+#define RL_TRACE_N 256
+#define RL_STAMP(ev, idx)                                                               \
+  do {                                                                                  \
+    if (p.trace != nullptr && pair == 0 && (idx) < RL_TRACE_N)                          \
+      p.trace[((int)rank * 8 + (ev)) * RL_TRACE_N + (idx)] = clock64();                 \
+  } while (0)
+#define RL_DEBUG(bit) ((p.debug & (bit)) != 0)
+#else
+#define RL_STAMP(ev, idx) \
+  do {                    \
+  } while (0)
+#define RL_DEBUG(bit) false
+#endif
+
+template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_>
+struct PairCfg {
+  static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_, ASLOTS = ASLOTS_, TG = TG_, AMODE = AMODE_;
+  static constexpr int THREADS = 64 + 128 * TG + 128;
+  static constexpr int A_BYTES = 128 * 64 * 2;
+  static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the W tile
+  static constexpr int G_BYTES = 128;
+  static constexpr int EPI_BYTES = 128 * 64 * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_EPI = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_G = OFF_EPI + 2 * EPI_BYTES;
+  static constexpr int OFF_RS = OFF_G + (AMODE_ == A_TS_FOLD ? STAGES * G_BYTES : 0);
+  static constexpr int OFF_BAR = OFF_RS + TG * NACC * 128 * 4;
+  static constexpr int NUM_BARS = 3 * STAGES + 4 * NACC;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 64;  // no alignment slack: the kernel checks the base instead
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int A_COL0 = NACC * BN;
+  static_assert(AMODE == A_TS_FOLD || AMODE == A_SS_DIRECT, "pair kernel: TS fold or SS direct");
+  static_assert(BN % 64 == 0 && BN <= 256, "BN");
+  static_assert(B_BYTES % 1024 == 0, "W stage alignment");
+  static_assert(NACC == 1 || NACC == 2, "NACC");
+  // a ring slot is always served by the same transform group (parity waits alias otherwise), and a
+  // group that waits for the MMA which last read its A slot must itself be the one feeding that MMA
+  static_assert(STAGES % TG == 0 && (AMODE != A_TS_FOLD || (STAGES - ASLOTS) % TG == 0), "ring / group layout");
+  static_assert(AMODE != A_TS_FOLD || (ASLOTS <= STAGES && NACC * BN + 32 * ASLOTS <= 512), "TMEM budget");
+  static_assert(NACC * BN <= 512, "TMEM budget");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+template <class Cfg>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::THREADS, 1)
+prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_y, const PrefillParams p) {
+  constexpr int BN = Cfg::BN, NACC = Cfg::NACC, STAGES = Cfg::STAGES, ASLOTS = Cfg::ASLOTS, TG = Cfg::TG;
+  constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  const uint32_t sbase = smem_u32(smem);
+  if (sbase & 1023u) {
+    // swizzled tiles need a 1024-byte aligned base; every thread of both CTAs sees the same value
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)DEV_BAD_SMEM_ALIGNMENT);
+    return;
+  }
+  const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+  auto bar_fullA = [&](int s) { return bar0 + 8u * s; };
+  auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+  auto bar_tfull = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };
+  auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * STAGES + NACC + a); };
+  auto bar_rsfull = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 * NACC + a); };
+  auto bar_rsfree = [&](int a) { return bar0 + 8u * (3 * STAGES + 3 * NACC + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_MISC);
+  volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
+  float* rs = reinterpret_cast<float*>(smem + Cfg::OFF_RS);  // [TG][NACC][128] partial sums of squares
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
+  const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+  const int KB = (p.K + 63) >> 6;
+  const int total_tiles = p.m_tiles * p.n_tiles;  // 256 x BN tiles
+  const bool has_gamma = (p.gamma != nullptr);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_fullA(s), 1);
+      mbar_init(bar_ready(s), 2 + 8);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < NACC; ++a) {
+      mbar_init(bar_tfull(a), 1);
+      mbar_init(bar_tempty(a), 8);
+      mbar_init(bar_rsfull(a), 4 * TG);
+      mbar_init(bar_rsfree(a), 4);
+    }
+    ctl->abort = 0;
+    ctl->status = p.status;
+    fence_mbar_init();
+    prefetch_tmap(&tm_x);
+    prefetch_tmap(&tm_w);
+    prefetch_tmap(&tm_y);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    [[maybe_unused]] int jp = 0;
+    const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
+    for (int t = pair; ok && t < total_tiles; t += n_pairs) {
+      int mt, nt;
+      prefill_tile_coords(t, p, mt, nt);
+      for (int kb = 0; kb < KB; ++kb) {
+        if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
+        if (elect_one()) {
+          RL_STAMP(0, jp);
+          const int kvalid = min(64, p.K - kb * 64);
+          const uint32_t gbytes = (TS && has_gamma) ? (uint32_t)kvalid * 2u : 0u;
+          mbar_expect_tx(bar_fullA(s), Cfg::A_BYTES + gbytes);
+          tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, &tm_x, bar_fullA(s), kb * 64, mt * 256 + (int)rank * 128);
+          if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_fullA(s));
+          const uint32_t lead_ready = lead_ready0 + 8u * s;
+          mbar_expect_tx_cluster(lead_ready, Cfg::B_BYTES);
+          tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kb * 64,
+                           nt * BN + (int)rank * (BN / 2));
+        }
+        __syncwarp();
+        ++jp;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer (rank 0 only)
+    if (rank == 0) {
+      constexpr uint32_t idesc = make_idesc(256, BN, 1, 1);
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      const uint64_t bdesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_B);
+      const uint64_t adesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_A);
+      int s = 0, aslot = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it) {
+        const int acc = (NACC == 2) ? (it & 1) : 0;
+        const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+        if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1u, ctl, 1, 3 * STAGES + NACC + acc, it)) break;
+        if (lane == 0) RL_STAMP(5, it);
+        const uint32_t d = tmem_base + acc * BN;
+        // The issue loop sets the tensor cores' pace: one barrier wait per k-block, the poll for the
+        // next slot started before this slot's MMAs are issued, and one predicated issue block.
+        uint32_t ready_now = mbar_try_wait(bar_ready(s), ph);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!ready_now) {
+            if (!mbar_wait(bar_ready(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
+          }
+          if (lane == 0) RL_STAMP(2, it * KB + kb);
+          tc_fence_after();
+          const int sn = (s + 1 == STAGES) ? 0 : s + 1;
+          const uint32_t phn = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
+          ready_now = mbar_try_wait(bar_ready(sn), phn);  // next k-block (or the next tile's first)
+          if (TS) {
+            umma_kblock_ts_pair(d, tmem_base + Cfg::A_COL0 + aslot * 32, bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)),
+                                idesc, (uint32_t)(kb != 0), bar_empty(s), leader);
+          } else {
+            umma_kblock_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
+                                bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != 0), bar_empty(s),
+                                leader);
+          }
+          s = sn;
+          ph = phn;
+          if (++aslot == ASLOTS) aslot = 0;
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) umma_commit_pair_pred(bar_tfull(acc), leader);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 2 + 4 * TG) {
+    // ------------------------------------------------------------ transform (both CTAs)
+    const int grp = (warp - 2) >> 2;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t swz = (uint32_t)(row & 7);
+    const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
+    bool ok = true;
+    int it = 0;
+    int j_base = 0;
+    for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it, j_base += KB) {
+      const int acc = (NACC == 2) ? (it & 1) : 0;
+      const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      float2 ss2 = make_float2(0.f, 0.f);
+      for (int kb = (grp - j_base % TG + TG) % TG; kb < KB; kb += TG) {
+        const int j = j_base + kb;
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+        ok = mbar_wait(bar_fullA(s), ph, ctl, 2, s, kb);
+        if (TS && ASLOTS < STAGES && j >= ASLOTS) {
+          // the MMA that last read this A slot (k-block j - ASLOTS) must be done
+          const int jo = j - ASLOTS;
+          ok = ok && mbar_wait(bar_empty(jo % STAGES), (uint32_t)(jo / STAGES) & 1u, ctl, 2, 2 * STAGES + jo % STAGES, kb);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (q == 0 && lane == 0) RL_STAMP(3, j);
+        if (RL_DEBUG(1)) {  // experiment: no tile work at all
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead_ready0 + 8u * s);
+          continue;
+        }
+        const uint8_t* a_row = smem + Cfg::OFF_A + s * Cfg::A_BYTES + row * 128;
+        uint32_t v[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 u = *reinterpret_cast<const uint4*>(a_row + ((c ^ swz) << 4));
+          v[4 * c + 0] = u.x; v[4 * c + 1] = u.y; v[4 * c + 2] = u.z; v[4 * c + 3] = u.w;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) ffma2_sq(ss2, bf16lo(v[jj]), bf16hi(v[jj]));
+        if (TS) {
+          if (has_gamma) {
+            const uint4* g = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES);
+            const int kvalid = p.K - kb * 64;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              if (c * 8 < kvalid) {
+                const uint4 gv = g[c];
+                v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv.x);
+                v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv.y);
+                v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv.z);
+                v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv.w);
+              } else {
+                v[4 * c + 0] = v[4 * c + 1] = v[4 * c + 2] = v[4 * c + 3] = 0u;
+              }
+            }
+          }
+          __syncwarp();
+          tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::A_COL0 + (j % ASLOTS) * 32, v);
+          tmem_wait_st();
+          tc_fence_before();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_ready0 + 8u * s);
+        if (q == 0 && lane == 0) RL_STAMP(4, j);
+      }
+      if (!ok) break;
+      ok = mbar_wait(bar_rsfree(acc), aph ^ 1u, ctl, 2, 3 * STAGES + 3 * NACC + acc, it);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      rs[(grp * NACC + acc) * 128 + row] = ss2.x + ss2.y;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_rsfull(acc));
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t swz = (uint32_t)(row & 7);
+    const int epi_tid = threadIdx.x - (64 + 128 * TG);
+    const uint32_t lead_tempty0 = mapa_shared(bar_tempty(0), 0);
+    bool ok = true;
+    int it = 0;
+    uint32_t chunk_no = 0;
+    for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it) {
+      int mt, nt;
+      prefill_tile_coords(t, p, mt, nt);
+      const int acc = (NACC == 2) ? (it & 1) : 0;
+      const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, it) &&
+          mbar_wait(bar_rsfull(acc), aph, ctl, 3, 3 * STAGES + 2 * NACC + acc, it);
+      // named barriers have no time limit: one thread decides for the four warps whether to go on
+      named_bar_sync(3, 128);
+      if (epi_tid == 0) *epi_go = ctl->abort ? 0 : 1;
+      named_bar_sync(4, 128);
+      ok = (*epi_go != 0);
+      if (!ok) break;
+      if (epi_tid == 0) RL_STAMP(6, it);
+      tc_fence_after();
+      float ssum = 0.f;
+#pragma unroll
+      for (int g = 0; g < TG; ++g) ssum += rs[(g * NACC + acc) * 128 + row];
+      const float r = 1.0f / sqrtf(ssum / (float)p.K + p.eps);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_rsfree(acc));
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c, ++chunk_no) {
+        uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;
+        if (epi_tid == 0) tma_store_wait_read<1>();
+        named_bar_sync(1, 128);
+        uint32_t v0[32], v1[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 64, v0);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 64 + 32, v1);
+        tmem_wait_ld();
+        if (c == BN / 64 - 1) {
+          // accumulator drained into registers: the pair's MMA warp may start on it again
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+          if (epi_tid == 0) RL_STAMP(7, it);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(v0[8 * j + 0]) * r, __uint_as_float(v0[8 * j + 1]) * r);
+          o.y = pack_bf16x2(__uint_as_float(v0[8 * j + 2]) * r, __uint_as_float(v0[8 * j + 3]) * r);
+          o.z = pack_bf16x2(__uint_as_float(v0[8 * j + 4]) * r, __uint_as_float(v0[8 * j + 5]) * r);
+          o.w = pack_bf16x2(__uint_as_float(v0[8 * j + 6]) * r, __uint_as_float(v0[8 * j + 7]) * r);
+          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)j ^ swz) << 4)) = o;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(v1[8 * j + 0]) * r, __uint_as_float(v1[8 * j + 1]) * r);
+          o.y = pack_bf16x2(__uint_as_float(v1[8 * j + 2]) * r, __uint_as_float(v1[8 * j + 3]) * r);
+          o.z = pack_bf16x2(__uint_as_float(v1[8 * j + 4]) * r, __uint_as_float(v1[8 * j + 5]) * r);
+          o.w = pack_bf16x2(__uint_as_float(v1[8 * j + 6]) * r, __uint_as_float(v1[8 * j + 7]) * r);
+          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)(4 + j) ^ swz) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(2, 128);
+        if (epi_tid == 0) {
+          const int n0 = nt * BN + c * 64;
+          if (n0 < p.N) tma_store_2d(&tm_y, smem_u32(stage), n0, mt * 256 + (int)rank * 128);
+          tma_store_commit();
+        }
+      }
+    }
+    if (epi_tid == 0) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (ctl->abort) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while its peer may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace rl

@@ -14,7 +14,7 @@ namespace rl {
 // First 64 ints of the caller's workspace.  [0] = first error code recorded
 // (0 = none), [1] = role, [2] = barrier id, [3] = blockIdx.x, [4] = loop index.
 enum : int { RL_STATUS_INTS = 64 };
-enum DeviceError : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1 };
+enum DeviceError : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1, DEV_BAD_SMEM_ALIGNMENT = 2 };
 
 struct CtaCtl {            // lives in shared memory
   volatile int abort;      // set by the first waiter that times out
@@ -91,6 +91,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, CtaCtl*
                                           int idx) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx);
+}
+
+// One lane of a fully converged warp.  The TMA and MMA issue loops run with the whole warp
+// converged and only the issuing instructions predicated on this: a loop run by a single
+// lane inside a divergent branch keeps descriptors out of the uniform datapath and issues
+// several times slower.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+// all lanes wait; the result is warp-uniform
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, CtaCtl* ctl, int role, int bar_id,
+                                               int idx) {
+  const bool ok = mbar_wait(bar, parity, ctl, role, bar_id, idx);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // ---------------------------------------------------------------- proxies / fences
@@ -246,6 +266,137 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
       "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+
+
+// ---------------------------------------------------------------- CTA pairs (cluster of 2, tcgen05 cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  // default semantics (release at CTA scope): a cluster-scope release costs a full fence per arrival
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+// every thread of both CTAs
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose completion is counted on an mbarrier that may
+// live in the peer CTA of the pair (no multicast: each CTA fetches its own tile).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// One thread of the pair's rank-0 CTA issues the MMA for both CTAs: M = 256 rows (128 per CTA, A from
+// each CTA's own tensor memory or shared memory), B rows split half and half between the CTAs.
+__device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in every CTA of `mask` once all MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(mask)
+      : "memory");
+}
+
+// One k-block (K = 64 = four K = 16 steps) of the pair MMA plus the commit that releases its ring
+// slot, as a single predicated block: every lane of the converged warp executes it, only the lane
+// with leader != 0 issues.  Keeping the issue loop free of branches, votes and re-elections matters:
+// the loop shares its scheduler with busy transform warps and sets the tensor cores' pace.
+__device__ __forceinline__ void umma_kblock_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate, uint32_t commit_bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b1, b2, b3;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b16 m;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [a1], b1, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [a2], b2, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [a3], b3, %3, p;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%5], m;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void umma_kblock_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate, uint32_t commit_bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b1, b2, b3, a1, a2, a3;\n\t.reg .b16 m;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
+      "add.u64 a1, %1, 2;\n\tadd.u64 a2, %1, 4;\n\tadd.u64 a3, %1, 6;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a1, b1, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a2, b2, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a3, b3, %3, p;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%5], m;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_pred(uint32_t bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b16 m;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\tmov.b16 m, 3;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+      ::"r"(bar), "r"(leader)
+      : "memory");
+}
+// packed fp32 pair FMA (sm_100): acc.{x,y} += a.{x,y} * a.{x,y}
+__device__ __forceinline__ void ffma2_sq(float2& acc, float lo, float hi) {
+  asm("{\n\t.reg .b64 v, c;\n\t"
+      "mov.b64 v, {%2, %3};\n\tmov.b64 c, {%0, %1};\n\t"
+      "fma.rn.f32x2 c, v, v, c;\n\t"
+      "mov.b64 {%0, %1}, c;\n\t}"
+      : "+f"(acc.x), "+f"(acc.y)
+      : "f"(lo), "f"(hi));
 }
 
 // ---------------------------------------------------------------- descriptors

@@ -63,10 +63,16 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 
 
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
-                                     "prefill_ss_n128"])
+                                     "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
+                                     "prefill_pair_direct"])
 @pytest.mark.parametrize("has_gamma", [False, True])
-def test_every_prefill_variant(variant, has_gamma):
-    M, N, K = 384, 776, 448
+@pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
+def test_every_prefill_variant(variant, has_gamma, M, N, K):
+    if variant == "prefill_pair_direct" and has_gamma:
+        with pytest.raises(ValueError):   # that variant reads x straight from shared memory: no gamma fold
+            x, gm, W = orc.make_inputs(256, 256, 64, gamma=True)
+            kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, variant=variant)
+        return
     x, gm, W = orc.make_inputs(M, N, K, seed=11, gamma=has_gamma)
     ref = orc.reference_fp32(x, gm, W, 1e-6)
     assert orc.rel_max_err(run(x, gm, W, 1e-6, variant=variant), ref) <= BF16_TOL
@@ -174,6 +180,10 @@ def test_config3_decode(M):
     xp = torch.zeros(128, K, dtype=torch.bfloat16)
     xp[:M] = x
     yp = run(xp, gm, W, 1e-6, variant="prefill_ts_n192")[:M]
+    assert orc.rel_max_err(yp, y.float()) <= 1e-2
+    xp2 = torch.zeros(256, K, dtype=torch.bfloat16)
+    xp2[:M] = x
+    yp = run(xp2, gm, W, 1e-6, variant="prefill_pair_n256")[:M]
     assert orc.rel_max_err(yp, y.float()) <= 1e-2
 
 
