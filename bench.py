@@ -47,6 +47,7 @@ WORKLOADS = {
     "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor"),
     "mlp_shard4_16384x14336x8192": (16384, 14336, 8192, "tensor"),
     "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor"),
+    "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor"),   # e4m3 weights + per-channel scales
 }
 DEFAULT_WORKLOAD = "prefill_qkv_4096x6144x4096"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries (profiles/)
@@ -54,8 +55,8 @@ NCU_TRAFFIC_BYTES = {}
 L2_BYTES = 126 * 1024 * 1024
 
 
-def algorithmic_bytes(M, N, K):
-    return 2 * M * K + 2 * N * K + 2 * K + 2 * M * N
+def algorithmic_bytes(M, N, K, fp8=False):
+    return 2 * M * K + (1 if fp8 else 2) * N * K + (4 * N if fp8 else 0) + 2 * K + 2 * M * N
 
 
 def measured_peaks():
@@ -122,7 +123,7 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def make_buffers(M, N, K, dev, sets, seed):
+def make_buffers(M, N, K, dev, sets, seed, fp8=False):
     """`sets` independent (x, gamma, W, y) groups so that consecutive steps never find their inputs in L2."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     out = []
@@ -134,7 +135,12 @@ def make_buffers(M, N, K, dev, sets, seed):
         for n0 in range(0, N, 8192):
             n1 = min(N, n0 + 8192)
             W[n0:n1] = (torch.randn(n1 - n0, K, generator=g, dtype=torch.float32) * K ** -0.5).to(torch.bfloat16)
-        out.append((x.to(dev), gamma.to(dev), W.to(dev), torch.empty(M, N, dtype=torch.bfloat16, device=dev), x))
+        Wd, wsc = W.to(dev), None
+        if fp8:
+            # per-output-channel absmax / 448 scales, weights stored as e4m3 codes
+            wsc = (Wd.float().abs().amax(dim=1) / 448.0).clamp_min(1e-30)
+            Wd = (Wd.float() / wsc[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+        out.append((x.to(dev), gamma.to(dev), Wd, torch.empty(M, N, dtype=torch.bfloat16, device=dev), x, wsc))
     return out
 
 
@@ -223,14 +229,15 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     M, N, K, bound = WORKLOADS[args.workload]
-    step_bytes = algorithmic_bytes(M, N, K)
+    fp8 = args.workload.startswith("fp8w")
+    step_bytes = algorithmic_bytes(M, N, K, fp8)
     sets = max(2, -(-2 * L2_BYTES // step_bytes))   # rotate enough buffer sets to exceed 2x L2
-    bufs = make_buffers(M, N, K, dev, sets, seed=18 + rank)
+    bufs = make_buffers(M, N, K, dev, sets, seed=18 + rank, fp8=fp8)
     stream = torch.cuda.current_stream()
 
     def step(i):
-        x, g, W, y, _ = bufs[i % sets]
-        kb.rmsnorm_linear(x, g, W, 1e-6, out=y, variant=args.variant)
+        x, g, W, y, _, wsc = bufs[i % sets]
+        kb.rmsnorm_linear(x, g, W, 1e-6, w_scale=wsc, out=y, variant=args.variant)
 
     def barrier():
         if world > 1:
@@ -286,9 +293,9 @@ def main():
     y_host = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
     def e2e_step(i):
-        x, g, W, y, _ = bufs[i % sets]
+        x, g, W, y, _, wsc = bufs[i % sets]
         x.copy_(x_host[i % 2], non_blocking=True)
-        kb.rmsnorm_linear(x, g, W, 1e-6, out=y, variant=args.variant)
+        kb.rmsnorm_linear(x, g, W, 1e-6, w_scale=wsc, out=y, variant=args.variant)
         y_host[i % 2].copy_(y, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 20))
@@ -330,13 +337,13 @@ def main():
         peaks = measured_peaks()
         per_gpu_ms = ms_step
         if bound == "tensor":
-            achieved, peak, r_unit = flops / (per_gpu_ms * 1e-3) / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+            achieved, peak, r_unit = flops / (per_gpu_ms * 1e-3) / 1e12, peaks["bf16_tflops"] * (2 if fp8 else 1), "TFLOP/s"
         else:
             achieved, peak, r_unit = step_bytes / (per_gpu_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
         line = {
             "metric": metric_name(bound), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)" if fp8 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "M": M, "N_per_gpu": N, "K": K, "eps": 1e-6, "gamma": True,
                        "sharding": f"column-parallel x{world}, x replicated, no collective",
                        "l2": f"inputs larger than L2: {sets} rotating buffer sets of {step_bytes / 1e6:.0f} MB",
@@ -345,9 +352,9 @@ def main():
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N,
                     "ms_per_step": e2e_ms, "note": "x from pinned host memory and y back to pinned host memory every "
                     "step; W and gamma are weights, resident on the device"},
-            "gpu_launches": args.steps * world,
+            "gpu_launches": args.steps * world * (2 if fp8 else 1),
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peaks['source']}",
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peaks['source']}" + (" bf16 x 2 (no FP8 peak was measured)" if fp8 else ""),
                          "algorithmic_bytes": step_bytes, "algorithmic_flops": flops},
         }
         if gather_ms is not None:

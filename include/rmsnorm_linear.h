@@ -84,6 +84,25 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
                            float eps, void* workspace, size_t workspace_bytes,
                            int variant, void* stream);
 
+/* FP8-weight fused RMSNorm -> Linear (quantised-inference path).
+ *   x [M, K] bf16, gamma [K] bf16 or NULL, Wq [N, K] e4m3 codes row-major (ldw bytes = elements),
+ *   w_scale [N] fp32 per-output-channel scales (W = Wq * w_scale[n]), y [M, N] bf16.
+ *   The normalised activations are quantised to e4m3 per token on the device:
+ *   q = e4m3(x * gamma * 448 / amax_m); y = (q @ Wq^T) * rsqrt(mean x^2 + eps) * amax_m / 448 * w_scale[n].
+ *   K and ldw must be multiples of 16.  The workspace (rl_workspace_bytes with RL_W_E4M3) holds
+ *   the quantised activations and the per-token scales.
+ * No reference counterpart: the reference project has no quantised path; the operator semantics
+ * are those of rl_rmsnorm_linear_bf16 applied to the dequantised weights. */
+int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, const float* w_scale, void* y,
+                           int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
+                           float eps, void* workspace, size_t workspace_bytes,
+                           int variant, void* stream);
+
+/* The first kernel of the FP8 path on its own: per row, q = e4m3(x * gamma * 448 / amax) into
+ * q [M, ldq] and row_scale[m] = rsqrt(mean x^2 + eps) * amax / 448.  No reference counterpart. */
+int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_scale,
+                          int M, int K, int64_t ldx, int64_t ldq, float eps, void* stream);
+
 /* Read the status block of a workspace (synchronises the stream's device: use
  * outside the hot loop).  Returns RL_OK or RL_ERR_DEVICE_TIMEOUT; when `detail`
  * is not NULL it receives 8 ints: code, role, barrier, block, index, parity, 0, 0.

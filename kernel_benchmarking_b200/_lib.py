@@ -48,6 +48,8 @@ SYMBOLS = [
     ("rl_workspace_bytes", _sz, [_i, _i, _i, _i]),
     ("rl_workspace_init", _i, [_vp, _sz, _vp]),
     ("rl_rmsnorm_linear_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
+    ("rl_rmsnorm_linear_fp8w", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
+    ("rl_quantize_rows_e4m3", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _f, _vp]),
     ("rl_read_status", _i, [_vp, ctypes.POINTER(ctypes.c_int)]),
 ]
 

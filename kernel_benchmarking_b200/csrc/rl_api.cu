@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "rl_decode.cuh"
+#include "rl_fp8_pair.cuh"
 #include "rl_prefill.cuh"
 #include "rl_prefill_pair.cuh"
 
@@ -207,6 +208,57 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+struct Fp8WsLayout {
+  size_t row_scale_off, xq_off, total;
+};
+Fp8WsLayout fp8_ws_layout(int M, int K) {
+  Fp8WsLayout w{};
+  w.row_scale_off = STATUS_BYTES;
+  w.xq_off = align_up(w.row_scale_off + (size_t)M * 4, 1024);
+  w.total = w.xq_off + (size_t)M * (size_t)K;
+  return w;
+}
+
+int launch_rowquant(const void* x, const void* gamma, void* q, float* row_scale, int M, int K, int64_t ldx,
+                    int64_t ldq, float eps, cudaStream_t st) {
+  RowQuantParams p{};
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  p.q = reinterpret_cast<uint8_t*>(q);
+  p.row_scale = row_scale;
+  p.M = M; p.K = K; p.ldx = ldx; p.ldq = ldq; p.eps = eps;
+  rowquant_kernel<<<M, 128, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
+template <class Cfg>
+int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, const float* w_scale, void* y, int M, int N,
+                    int K, int64_t ldq, int64_t ldw, int64_t ldy, int* status, int sms, cudaStream_t st) {
+  CUtensorMap ta, tw, ty;
+  int rc;
+  if ((rc = make_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, K, M, ldq, 128, 128))) return rc;
+  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, K, N, ldw, 128, 128))) return rc;
+  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
+  Fp8GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.row_scale = row_scale;
+  p.w_scale = w_scale;
+  p.m_tiles = (M + 255) / 256;
+  p.n_tiles = (N + 255) / 256;
+  p.group_m = 8;
+  p.status = status;
+  cudaError_t e = cudaFuncSetAttribute(fp8_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_err(e);
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const int max_pairs = sms / 2;
+  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  fp8_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ta, tw, ty, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
 }  // namespace
 
 extern "C" {
@@ -233,9 +285,8 @@ const char* rl_error_string(int code) {
 }
 
 size_t rl_workspace_bytes(int M, int N, int K, int w_dtype) {
-  (void)K;
-  (void)w_dtype;
-  if (M <= 0 || N <= 0) return STATUS_BYTES;
+  if (M <= 0 || N <= 0 || K <= 0) return STATUS_BYTES;
+  if (w_dtype == RL_W_E4M3) return fp8_ws_layout(M, K).total;
   return ws_layout(M, N).total;
 }
 
@@ -298,6 +349,39 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     default: return RL_ERR_BAD_VARIANT;
   }
 #undef RL_PREFILL
+}
+
+int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_scale, int M, int K, int64_t ldx,
+                          int64_t ldq, float eps, void* stream) {
+  if (!x || !q || !row_scale) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || K <= 0 || ldx < K || ldq < K) return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (ldx & 7) || (ldq & 7) || !aligned16(x) || !aligned16(q) || (gamma && !aligned16(gamma)))
+    return RL_ERR_ALIGNMENT;
+  return launch_rowquant(x, gamma, q, row_scale, M, K, ldx, ldq, eps, (cudaStream_t)stream);
+}
+
+int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, const float* w_scale, void* y, int M, int N,
+                           int K, int64_t ldx, int64_t ldw, int64_t ldy, float eps, void* workspace,
+                           size_t workspace_bytes, int variant, void* stream) {
+  if (!x || !Wq || !w_scale || !y) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return RL_ERR_BAD_SHAPE;
+  if ((K & 15) || (ldx & 7) || (ldw & 15) || (ldy & 7) || !aligned16(x) || !aligned16(Wq) || !aligned16(y) ||
+      (gamma && !aligned16(gamma)))
+    return RL_ERR_ALIGNMENT;
+  if (variant != RL_VARIANT_AUTO) return RL_ERR_BAD_VARIANT;
+  const Fp8WsLayout wl = fp8_ws_layout(M, K);
+  if (!workspace || workspace_bytes < wl.total) return RL_ERR_WORKSPACE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  float* row_scale = reinterpret_cast<float*>(ws + wl.row_scale_off);
+  uint8_t* xq = ws + wl.xq_off;
+  if ((rc = launch_rowquant(x, gamma, xq, row_scale, M, K, ldx, K, eps, st))) return rc;
+  return launch_fp8_pair<Fp8PairCfg<6>>(xq, row_scale, Wq, w_scale, y, M, N, K, K, ldw, ldy, reinterpret_cast<int*>(ws),
+                                        di.sms, st);
 }
 
 int rl_read_status(const void* workspace, int* detail) {

@@ -47,15 +47,29 @@ def _check_matrix(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
 
 
 def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tensor, eps: float = 1e-6, *,
-                   out: Optional[torch.Tensor] = None, variant: str | int = "auto") -> torch.Tensor:
+                   w_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                   variant: str | int = "auto") -> torch.Tensor:
     """y = rms_norm(x, weight=gamma, eps) @ W.t() in one fused sm_100a kernel.
 
     x [M, K] bf16, gamma [K] bf16 or None (None = ones, which is the reference operator:
     `F.rms_norm(a, (K,), eps=eps) @ b.t()`, demo/rmsnorm_linear.py:36-38), W [N, K] bf16.
     Returns y [M, N] bf16 (fp32 accumulation).  Runs on the current CUDA stream, asynchronously.
+
+    Quantised-inference path: W of dtype float8_e4m3fn with `w_scale` [N] fp32 per-output-channel
+    scales (W_real = W * w_scale[:, None]); the normalised activations are quantised to e4m3 per
+    token on the device.
     """
     _check_matrix("x", x, torch.bfloat16)
-    _check_matrix("W", W, torch.bfloat16)
+    fp8 = isinstance(W, torch.Tensor) and W.dtype == torch.float8_e4m3fn
+    _check_matrix("W", W, torch.float8_e4m3fn if fp8 else torch.bfloat16)
+    if fp8:
+        if w_scale is None:
+            raise ValueError("e4m3 weights need w_scale (fp32, one scale per output channel)")
+        if (not w_scale.is_cuda or w_scale.device != x.device or w_scale.dtype != torch.float32
+                or w_scale.dim() != 1 or w_scale.shape[0] != W.shape[0] or w_scale.stride(0) != 1):
+            raise ValueError("w_scale must be a contiguous fp32 CUDA vector of length N on x's device")
+    elif w_scale is not None:
+        raise ValueError("w_scale is only meaningful with float8_e4m3fn weights")
     M, K = x.shape
     N, K2 = W.shape
     if K2 != K:
@@ -80,6 +94,15 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
     v = _lib.VARIANTS[variant] if isinstance(variant, str) else int(variant)
     lib = _lib.load()
     stream = _stream_ptr()
+    if fp8:
+        with torch.cuda.device(x.device):
+            ws = _workspace(x.device, lib.rl_workspace_bytes(M, N, K, _lib.RL_W_E4M3), stream)
+            rc = lib.rl_rmsnorm_linear_fp8w(
+                x.data_ptr(), None if gamma is None else gamma.data_ptr(), W.data_ptr(), w_scale.data_ptr(),
+                out.data_ptr(), M, N, K, x.stride(0), W.stride(0), out.stride(0), ctypes.c_float(eps),
+                ws.data_ptr(), ws.numel(), v, stream)
+        _lib.check(rc, "rl_rmsnorm_linear_fp8w")
+        return out
     with torch.cuda.device(x.device):
         ws = _workspace(x.device, lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16), stream)
         rc = lib.rl_rmsnorm_linear_bf16(
@@ -88,6 +111,20 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
             ws.data_ptr(), ws.numel(), v, stream)
     _lib.check(rc, "rl_rmsnorm_linear_bf16")
     return out
+
+
+def quantize_rows_e4m3(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float = 1e-6):
+    """First kernel of the FP8 path on its own: returns (q [M, K] float8_e4m3fn, row_scale [M] fp32) with
+    q = e4m3(x * gamma * 448 / amax_row) and row_scale = rsqrt(mean x^2 + eps) * amax_row / 448."""
+    _check_matrix("x", x, torch.bfloat16)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    rs = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().rl_quantize_rows_e4m3(x.data_ptr(), None if gamma is None else gamma.data_ptr(), q.data_ptr(),
+                                               rs.data_ptr(), M, K, x.stride(0), K, ctypes.c_float(eps), _stream_ptr())
+    _lib.check(rc, "rl_quantize_rows_e4m3")
+    return q.view(torch.float8_e4m3fn), rs
 
 
 def check_status(device: Optional[torch.device] = None) -> None:

@@ -158,7 +158,9 @@ def fp8_kernel_model(x: torch.Tensor, gamma: torch.Tensor | None, Wq: torch.Tens
     x32 = x.float()
     xg = x32 if gamma is None else x32 * gamma.float()
     amax = xg.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
-    q = (xg * (E4M3_MAX / amax)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).float()
+    # tensor / tensor is an IEEE division; `scalar / tensor` in torch is reciprocal-then-multiply (two roundings)
+    qs = torch.full_like(amax, E4M3_MAX) / amax
+    q = (xg * qs).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).float()
     acc = q @ Wq.float().t()
     r = torch.rsqrt(x32.pow(2).mean(dim=1, keepdim=True) + eps)
     y = acc * (r * amax / E4M3_MAX) * w_scale.float()[None, :]

@@ -206,3 +206,94 @@ def test_config4_one_of_eight_shards():
     assert worst <= BF16_TOL
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(r))[:16]
     assert _sample_check(x, gm, Wl, y.cpu(), 1e-6, rows) <= BF16_TOL
+
+
+# ---------------------------------------------------------------- FP8-weight path
+FP8_TOL = 3e-2        # at the benchmark's K = 4096
+FP8_TOL_SMALL_K = 5e-2  # fewer terms per output average less of the e4m3 rounding noise
+
+
+def run_fp8(x, g, Wq, w_scale, eps):
+    y = kb.rmsnorm_linear(x.to(DEV), None if g is None else g.to(DEV), Wq.to(DEV), eps, w_scale=w_scale.to(DEV))
+    torch.cuda.synchronize()
+    kb.check_status()
+    return y.cpu()
+
+
+def test_fp8_golden_vector(golden_dir):
+    g = np.load(os.path.join(golden_dir, "fp8w_32x64x256.npz"))
+    x, gm = bf16(g["x_bits"]), bf16(g["gamma_bits"])
+    Wq = torch.from_numpy(g["Wq_codes"]).view(torch.float8_e4m3fn)
+    w_scale = torch.from_numpy(g["w_scale"])
+    y = run_fp8(x, gm, Wq, w_scale, float(g["eps"]))
+    assert orc.rel_max_err(y, torch.from_numpy(g["y_ref_fp64"])) <= FP8_TOL_SMALL_K
+
+
+@pytest.mark.parametrize("M,K,has_gamma", [(1, 64, True), (37, 256, True), (300, 4096, True), (64, 1024, False)])
+def test_row_quantisation_is_bit_exact(M, K, has_gamma):
+    """The pre-pass against the oracle's arithmetic: same e4m3 codes, same per-token scale."""
+    x, gm, _ = orc.make_inputs(M, 8, K, seed=K + M, gamma=has_gamma)
+    q, rs = kb.quantize_rows_e4m3(x.to(DEV), None if gm is None else gm.to(DEV), 1e-6)
+    x32 = x.float()
+    xg = x32 if gm is None else x32 * gm.float()
+    amax = xg.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    qs = torch.full_like(amax, 448.0) / amax          # IEEE division, as on the device
+    q_ref = (xg * qs).clamp(-448, 448).to(torch.float8_e4m3fn)
+    rs_ref = torch.rsqrt(x32.pow(2).mean(dim=1) + 1e-6) * amax[:, 0] / 448.0
+    codes, codes_ref = q.cpu().view(torch.uint8), q_ref.view(torch.uint8)
+    same = (codes == codes_ref) | ((codes & 0x7F) == 0) & ((codes_ref & 0x7F) == 0)   # +0 / -0
+    # The device's cvt.rn.satfinite and torch's CPU cast may pick different neighbours for a value that
+    # sits (to fp32 precision) on a rounding boundary: such codes must be adjacent and very rare.
+    if not bool(same.all()):
+        d = (codes.int() - codes_ref.int()).abs()[~same]
+        assert int(d.max()) <= 1, "a quantised activation is off by more than one e4m3 step"
+        assert float((~same).float().mean()) <= 1e-4, f"{int((~same).sum())} of {same.numel()} codes differ"
+    torch.testing.assert_close(rs.cpu(), rs_ref, rtol=2e-6, atol=0)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 2048), (1000, 1032, 4096), (5, 264, 1024)])
+def test_fp8_shapes(M, N, K):
+    x, gm, W = orc.make_inputs(M, N, K, seed=M + N)
+    Wq, w_scale = orc.quantize_weight_e4m3(W)
+    y = run_fp8(x, gm, Wq, w_scale, 1e-6)
+    ref = orc.reference_fp32(x, gm, Wq, 1e-6, w_scale=w_scale)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert orc.rel_max_err(y, ref) <= (FP8_TOL if K >= 4096 else FP8_TOL_SMALL_K)
+    # the kernels follow the oracle's arithmetic model to bf16 rounding
+    assert orc.rel_max_err(y, orc.fp8_kernel_model(x, gm, Wq, w_scale, 1e-6).float()) <= 1e-2
+
+
+def test_config5_fp8_weights():
+    M, N, K = 8192, 14336, 4096
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    gm = (1 + 0.1 * torch.randn(K, generator=g)).bfloat16()
+    W = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16()
+    Wq, w_scale = orc.quantize_weight_e4m3(W)
+    xd, gd, Wqd, wsd = x.to(DEV), gm.to(DEV), Wq.to(DEV), w_scale.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd)
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    Wdq = Wqd.float() * wsd[:, None]
+    # the metric over the whole tensor: max |y - y_ref| / max |y_ref|, y_ref by torch fp32 on the GPU in slabs
+    max_err, max_ref = 0.0, 0.0
+    for m0 in range(0, M, 1024):
+        ref = orc.torch_rmsnorm_linear(xd[m0:m0 + 1024].float(), gd.float(), Wdq, 1e-6)
+        max_err = max(max_err, float((y[m0:m0 + 1024].float() - ref).abs().max()))
+        max_ref = max(max_ref, float(ref.abs().max()))
+    assert max_err / max_ref <= FP8_TOL
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(5))[:16]
+    # the CPU oracle on a row sample, against the same denominator (a 16-row sample's own max is much noisier)
+    ref = orc.reference_fp32(x[rows], gm, Wq, 1e-6, w_scale=w_scale)
+    assert float((y.cpu()[rows].float() - ref).abs().max()) / max_ref <= FP8_TOL
+    assert torch.equal(kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd), y)
+
+
+def test_fp8_bad_arguments():
+    x, gm, W = orc.make_inputs(16, 64, 64)
+    Wq, w_scale = orc.quantize_weight_e4m3(W)
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), Wq.to(DEV), 1e-6)                 # scales missing
+    with pytest.raises(ValueError):
+        kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, w_scale=w_scale.to(DEV))  # scales with bf16 W
