@@ -31,6 +31,7 @@ enum {
   RL_ERR_BAD_VARIANT = -7,      /* unknown kernel variant, or one that cannot run this shape */
   RL_ERR_TENSOR_MAP = -8,       /* the driver rejected a TMA descriptor */
   RL_ERR_DEVICE_TIMEOUT = -9,   /* a bounded wait inside a kernel ran out (reported by rl_read_status) */
+  RL_ERR_STATIC_SCRATCH = -10,  /* rl_rmsnorm_linear_bf16_noalloc: the shape needs more scratch than the built-in buffer */
   RL_ERR_CUDA = -1000           /* RL_ERR_CUDA - cudaError_t of the failing runtime call */
 };
 
@@ -102,6 +103,31 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
  * q [M, ldq] and row_scale[m] = rsqrt(mean x^2 + eps) * amax / 448.  No reference counterpart. */
 int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_scale,
                           int M, int K, int64_t ldx, int64_t ldq, float eps, void* stream);
+
+/* The small-M kernel for callers that cannot allocate.
+ *
+ * rl_rmsnorm_linear_bf16 needs a caller-provided workspace for M <= 64, which means the caller
+ * must be able to obtain device memory.  Some callers cannot: a plug-in that is handed raw input and
+ * output pointers by a host engine which has already claimed all device memory for its own arena; a
+ * component that is forbidden to touch the CUDA allocator because cudaMalloc / cudaFree synchronise
+ * the whole device and would stall the engine's other streams; a bare C caller with no allocator at
+ * hand.  For them this entry point takes only inputs and outputs and keeps its scratch (status block,
+ * tile counters, split-K partial tiles) in a 3 MiB array that is part of the library's device image.
+ * It calls no cudaMalloc, cudaFree or allocating library routine.
+ *
+ *   - Limit: M <= 16 tokens (any N and K the small-M kernel accepts); larger M returns
+ *     RL_ERR_STATIC_SCRATCH.  The 3 MiB stay resident on every GPU that loads the library until exit.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ *     should therefore be made, once per device, before any stream capture begins.
+ *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *     streams, or different host threads on different streams) race on it.  Serialise them on one
+ *     stream.  The part that must start from zero is cleared on `stream` before every launch.
+ *   - Arguments and results are those of rl_rmsnorm_linear_bf16; device-side timeouts are recorded in
+ *     the internal array and are not retrievable through rl_read_status.
+ * This function has no counterpart in the reference project. */
+int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void* W, void* y,
+                                   int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
+                                   float eps, void* stream);
 
 /* Read the status block of a workspace (synchronises the stream's device: use
  * outside the hot loop).  Returns RL_OK or RL_ERR_DEVICE_TIMEOUT; when `detail`

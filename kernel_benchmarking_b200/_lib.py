@@ -20,6 +20,7 @@ RL_ERR_UNSUPPORTED_ARCH = -6
 RL_ERR_BAD_VARIANT = -7
 RL_ERR_TENSOR_MAP = -8
 RL_ERR_DEVICE_TIMEOUT = -9
+RL_ERR_STATIC_SCRATCH = -10
 RL_ERR_CUDA = -1000
 
 RL_W_BF16 = 0
@@ -50,6 +51,7 @@ SYMBOLS = [
     ("rl_rmsnorm_linear_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
     ("rl_rmsnorm_linear_fp8w", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
     ("rl_quantize_rows_e4m3", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _f, _vp]),
+    ("rl_rmsnorm_linear_bf16_noalloc", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp]),
     ("rl_read_status", _i, [_vp, ctypes.POINTER(ctypes.c_int)]),
 ]
 
@@ -83,6 +85,7 @@ def check(code: int, what: str) -> None:
     if code == RL_OK:
         return
     msg = f"{what}: {error_string(code)} (code {code})"
-    if code in (RL_ERR_NULL_POINTER, RL_ERR_BAD_SHAPE, RL_ERR_ALIGNMENT, RL_ERR_BAD_DTYPE, RL_ERR_BAD_VARIANT):
+    if code in (RL_ERR_NULL_POINTER, RL_ERR_BAD_SHAPE, RL_ERR_ALIGNMENT, RL_ERR_BAD_DTYPE, RL_ERR_BAD_VARIANT,
+                RL_ERR_STATIC_SCRATCH):
         raise ValueError(msg)
     raise RuntimeError(msg)

@@ -259,6 +259,32 @@ int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, cons
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+// ---- scratch for the allocation-free entry point: lives in the library's device image, one copy per
+// GPU that loads the library, held until the process exits.  In host code this name is only a handle
+// for cudaGetSymbolAddress, never a device address to pass to a kernel.
+constexpr size_t RL_STATIC_SCRATCH_BYTES = 3u << 20;  // 3 MiB: enough for M <= 16 tokens, any N the decode kernel takes
+static __device__ __align__(256) unsigned char g_static_scratch[RL_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+int static_scratch_address(uint8_t** out) {
+  static std::mutex mu;
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_err(e);
+  if (dev < 0 || dev >= 64) return RL_ERR_UNSUPPORTED_ARCH;
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_err(e);
+    if (ptr == nullptr) return RL_ERR_WORKSPACE;
+    cache[dev] = ptr;
+  }
+  *out = reinterpret_cast<uint8_t*>(cache[dev]);
+  return RL_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -278,6 +304,8 @@ const char* rl_error_string(int code) {
     case RL_ERR_BAD_VARIANT: return "unknown kernel variant, or one that cannot run this shape";
     case RL_ERR_TENSOR_MAP: return "the driver rejected a TMA descriptor";
     case RL_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out of time";
+    case RL_ERR_STATIC_SCRATCH:
+      return "shape exceeds the built-in scratch of the allocation-free entry point (M <= 16 tokens)";
     default: break;
   }
   if (code <= RL_ERR_CUDA) return cudaGetErrorString((cudaError_t)(RL_ERR_CUDA - code));
@@ -382,6 +410,31 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
   if ((rc = launch_rowquant(x, gamma, xq, row_scale, M, K, ldx, K, eps, st))) return rc;
   return launch_fp8_pair<Fp8PairCfg<6>>(xq, row_scale, Wq, w_scale, y, M, N, K, K, ldw, ldy, reinterpret_cast<int*>(ws),
                                         di.sms, st);
+}
+
+int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void* W, void* y, int M, int N, int K,
+                                   int64_t ldx, int64_t ldw, int64_t ldy, float eps, void* stream) {
+  if (!x || !W || !y) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (ldx & 7) || (ldw & 7) || !aligned16(x) || !aligned16(W) || (gamma && !aligned16(gamma)))
+    return RL_ERR_ALIGNMENT;
+  // the built-in scratch is sized for the 16-token configuration of the small-M kernel
+  if (M > 16) return RL_ERR_STATIC_SCRATCH;
+  const WsLayout wl = ws_layout(M, N);
+  if (wl.total > RL_STATIC_SCRATCH_BYTES) return RL_ERR_STATIC_SCRATCH;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  uint8_t* scratch = nullptr;
+  if ((rc = static_scratch_address(&scratch))) return rc;  // first call on a device resolves the symbol
+  cudaStream_t st = (cudaStream_t)stream;
+  // The array keeps whatever the previous call left.  The status block and the tile counters must start
+  // at zero; partial tiles are always written before they are read and need no clearing.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, wl.ssq_off, st);
+  if (e != cudaSuccess) return cuda_err(e);
+  return launch_decode<DecodeCfg<16, 12>>(x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw,
+                                          ldy, eps, scratch, wl, di.sms, st);
 }
 
 int rl_read_status(const void* workspace, int* detail) {
