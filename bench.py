@@ -147,6 +147,7 @@ def make_buffers(M, N, K, dev, sets, seed, fp8=False):
 def cpu_reference_time(M, N, K, budget_s=15.0):
     """The reference's torch path on the host cores, fp32, on a row sample sized to ~budget_s."""
     from oracle import rmsnorm_linear_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
     rows = min(M, 512)
     x, gm, W = orc.make_inputs(rows, N, K, seed=18, dtype=torch.float32)
     orc.torch_rmsnorm_linear(x, gm, W, 1e-6)   # warm-up
@@ -165,6 +166,8 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     M, N, K, bound = WORKLOADS[args.workload]
+    # all host cores (torchrun pins OMP_NUM_THREADS=1 for its workers; only rank 0 works here)
+    torch.set_num_threads(os.cpu_count() or 1)
     # bounded sample per step: min(M, 512) rows of the workload, all N and K
     from oracle import rmsnorm_linear_oracle as orc
     rows = min(M, 512)

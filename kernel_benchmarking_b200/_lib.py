@@ -36,7 +36,8 @@ VARIANTS = {
     "prefill_pair_n256": 9,
     "prefill_pair_n192": 10,
     "prefill_pair_direct": 11,
-    "x12": 12, "x13": 13,
+    "prefill_pair_prestats": 14,
+    "x12": 12, "x13": 13, "x15": 15,
     "x6": 6, "x7": 7, "x8": 8,
     "decode": 20,
 }

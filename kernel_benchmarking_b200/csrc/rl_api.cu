@@ -87,7 +87,7 @@ struct WsLayout {
 WsLayout ws_layout(int M, int N) {
   WsLayout w{};
   if (M > 64) {
-    w.total = STATUS_BYTES;
+    w.total = STATUS_BYTES + align_up((size_t)M * 4, 256);  // status block + 1/rms per token (PRESTATS kernels)
     return w;
   }
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -140,6 +140,12 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.n_tiles = (N + Cfg::BN - 1) / Cfg::BN;
   p.group_m = 8;
   p.status = status;
+  if (Cfg::PRESTATS) {
+    if (status == nullptr) return RL_ERR_WORKSPACE;
+    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + STATUS_BYTES);
+    rowstats_kernel<<<(M + 3) / 4, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), rstd, M, K, ldx, eps);
+    p.row_rstd = rstd;
+  }
 #ifdef RL_TRACE
   p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
   p.trace = status ? reinterpret_cast<long long*>(reinterpret_cast<uint8_t*>(status) + 4096) : nullptr;
@@ -363,13 +369,16 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD, 1) : RL_PREFILL(256, 4, A_SS_DIRECT, 1);
     case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 4, A_TS_FOLD, 2);
     case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 4, A_SS_FOLD, 2) : RL_PREFILL(128, 4, A_SS_DIRECT, 2);
-#define RL_PAIR(BN, NACC, ST, AS, TG, AM) \
-  launch_prefill_pair<PairCfg<BN, NACC, ST, AS, TG, AM>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
+#define RL_PAIR(BN, NACC, ST, AS, TG, AM, ...) \
+  launch_prefill_pair<PairCfg<BN, NACC, ST, AS, TG, AM, ##__VA_ARGS__>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, \
+                                                                       di.sms, st)
     case RL_VARIANT_PREFILL_PAIR_N256: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
+    case RL_VARIANT_PREFILL_PAIR_PRESTATS: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
     case 12: return RL_PAIR(192, 2, 6, 3, 3, A_TS_FOLD);
     case 13: return RL_PAIR(256, 1, 6, 6, 3, A_TS_FOLD);
+    case 15: return RL_PAIR(256, 1, 6, 6, 1, A_TS_FOLD, true);
 #undef RL_PAIR
     case 6: return RL_PREFILL(192, 3, A_TS_FOLD, 1);
     case 7: return RL_PREFILL(192, 2, A_TS_FOLD, 1);

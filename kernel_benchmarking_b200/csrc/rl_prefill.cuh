@@ -29,7 +29,45 @@ struct PrefillParams {
   int* status;  // RL_STATUS_INTS ints or nullptr
   long long* trace;  // timeline stamps of CTA pair 0 (only read by builds with RL_TRACE)
   int debug;         // experiment switches, honoured only by builds with RL_TRACE (results become wrong)
+  const float* row_rstd;  // [M] 1/rms per token from rowstats_kernel (kernels built with PRESTATS), else nullptr
 };
+
+// Row statistics on their own: rstd[m] = rsqrt(mean_k x[m,k]^2 + eps).  One warp per token row, 16-byte
+// loads, butterfly reduction.  Used by the PRESTATS kernels, where every column tile would otherwise
+// recompute the same sums of squares (N/256 times per row).
+__global__ void __launch_bounds__(128) rowstats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ rstd,
+                                                       int M, int K, long long ldx, float eps) {
+  const int m = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)m * ldx);
+  const int chunks = K >> 3;
+  float2 acc = make_float2(0.f, 0.f);
+  int c = lane;
+  for (; c + 96 < chunks; c += 128) {  // four independent 16-byte loads in flight per lane
+    uint4 u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) u[i] = xr[c + 32 * i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ffma2_sq(acc, bf16lo(u[i].x), bf16hi(u[i].x));
+      ffma2_sq(acc, bf16lo(u[i].y), bf16hi(u[i].y));
+      ffma2_sq(acc, bf16lo(u[i].z), bf16hi(u[i].z));
+      ffma2_sq(acc, bf16lo(u[i].w), bf16hi(u[i].w));
+    }
+  }
+  for (; c < chunks; c += 32) {
+    const uint4 u = xr[c];
+    ffma2_sq(acc, bf16lo(u.x), bf16hi(u.x));
+    ffma2_sq(acc, bf16lo(u.y), bf16hi(u.y));
+    ffma2_sq(acc, bf16lo(u.z), bf16hi(u.z));
+    ffma2_sq(acc, bf16lo(u.w), bf16hi(u.w));
+  }
+  float s = acc.x + acc.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) rstd[m] = 1.0f / sqrtf(s / (float)K + eps);
+}
 
 template <int BN_, int STAGES_, int AMODE_, int TG_ = 2>
 struct PrefillCfg {

@@ -47,9 +47,11 @@ namespace rl {
 #define RL_DEBUG(bit) false
 #endif
 
-template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_>
+template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false>
 struct PairCfg {
   static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_, ASLOTS = ASLOTS_, TG = TG_, AMODE = AMODE_;
+  // PRESTATS: 1/rms per token comes from rowstats_kernel; the transform warps only fold gamma
+  static constexpr bool PRESTATS = PRESTATS_;
   static constexpr int THREADS = 64 + 128 * TG + 128;
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the W tile
@@ -84,6 +86,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const __grid_constant__ CUtensorMap tm_y, const PrefillParams p) {
   constexpr int BN = Cfg::BN, NACC = Cfg::NACC, STAGES = Cfg::STAGES, ASLOTS = Cfg::ASLOTS, TG = Cfg::TG;
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
+  constexpr bool PRESTATS = Cfg::PRESTATS;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
@@ -255,8 +258,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           const uint4 u = *reinterpret_cast<const uint4*>(a_row + ((c ^ swz) << 4));
           v[4 * c + 0] = u.x; v[4 * c + 1] = u.y; v[4 * c + 2] = u.z; v[4 * c + 3] = u.w;
         }
+        if (!PRESTATS) {
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) ffma2_sq(ss2, bf16lo(v[jj]), bf16hi(v[jj]));
+          for (int jj = 0; jj < 32; ++jj) ffma2_sq(ss2, bf16lo(v[jj]), bf16hi(v[jj]));
+        }
         if (TS) {
           if (has_gamma) {
             const uint4* g = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES);
@@ -284,12 +289,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (q == 0 && lane == 0) RL_STAMP(4, j);
       }
       if (!ok) break;
-      ok = mbar_wait(bar_rsfree(acc), aph ^ 1u, ctl, 2, 3 * STAGES + 3 * NACC + acc, it);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      rs[(grp * NACC + acc) * 128 + row] = ss2.x + ss2.y;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_rsfull(acc));
+      if (!PRESTATS) {
+        ok = mbar_wait(bar_rsfree(acc), aph ^ 1u, ctl, 2, 3 * STAGES + 3 * NACC + acc, it);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        rs[(grp * NACC + acc) * 128 + row] = ss2.x + ss2.y;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rsfull(acc));
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
@@ -306,8 +313,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       prefill_tile_coords(t, p, mt, nt);
       const int acc = (NACC == 2) ? (it & 1) : 0;
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      float r_pre = 0.f;
+      if (PRESTATS) {
+        const int m = mt * 256 + (int)rank * 128 + row;
+        r_pre = (m < p.M) ? __ldg(p.row_rstd + m) : 0.f;
+      }
       mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, it) &&
-          mbar_wait(bar_rsfull(acc), aph, ctl, 3, 3 * STAGES + 2 * NACC + acc, it);
+          (PRESTATS || mbar_wait(bar_rsfull(acc), aph, ctl, 3, 3 * STAGES + 2 * NACC + acc, it));
       // named barriers have no time limit: one thread decides for the four warps whether to go on
       named_bar_sync(3, 128);
       if (epi_tid == 0) *epi_go = ctl->abort ? 0 : 1;
@@ -316,12 +328,15 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       if (!ok) break;
       if (epi_tid == 0) RL_STAMP(6, it);
       tc_fence_after();
-      float ssum = 0.f;
+      float r = r_pre;
+      if (!PRESTATS) {
+        float ssum = 0.f;
 #pragma unroll
-      for (int g = 0; g < TG; ++g) ssum += rs[(g * NACC + acc) * 128 + row];
-      const float r = 1.0f / sqrtf(ssum / (float)p.K + p.eps);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_rsfree(acc));
+        for (int g = 0; g < TG; ++g) ssum += rs[(g * NACC + acc) * 128 + row];
+        r = 1.0f / sqrtf(ssum / (float)p.K + p.eps);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rsfree(acc));
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c, ++chunk_no) {
         uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;

@@ -64,7 +64,7 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
                                      "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
-                                     "prefill_pair_direct"])
+                                     "prefill_pair_direct", "prefill_pair_prestats"])
 @pytest.mark.parametrize("has_gamma", [False, True])
 @pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
 def test_every_prefill_variant(variant, has_gamma, M, N, K):
