@@ -87,7 +87,9 @@ struct WsLayout {
 WsLayout ws_layout(int M, int N) {
   WsLayout w{};
   if (M > 64) {
-    w.total = STATUS_BYTES + align_up((size_t)M * 4, 256);  // status block + 1/rms per token (PRESTATS kernels)
+    // status block, the (untouched) tile-counter region every shape keeps at the same place, then 1/rms per
+    // token for the PRESTATS kernels
+    w.total = STATUS_BYTES + COUNTER_BYTES + align_up((size_t)M * 4, 256);
     return w;
   }
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -142,7 +144,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.status = status;
   if (Cfg::PRESTATS) {
     if (status == nullptr) return RL_ERR_WORKSPACE;
-    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + STATUS_BYTES);
+    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + STATUS_BYTES + COUNTER_BYTES);
     rowstats_kernel<<<(M + 3) / 4, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), rstd, M, K, ldx, eps);
     p.row_rstd = rstd;
   }
@@ -176,6 +178,22 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   }
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  if (Cfg::PRESTATS) {
+    // behind rowstats_kernel with programmatic stream serialisation: the GEMM streams its tiles while the
+    // row statistics are still being computed and waits only where it first reads them
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(2 * pairs));
+    lc.blockDim = dim3(Cfg::THREADS);
+    lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    e = cudaLaunchKernelEx(&lc, prefill_pair_kernel<Cfg>, tx, tw, ty, p);
+    return e == cudaSuccess ? RL_OK : cuda_err(e);
+  }
   prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? RL_OK : cuda_err(e);
@@ -209,8 +227,20 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   cudaError_t e = cudaFuncSetAttribute(decode_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
-  decode_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tw, tx, p);
-  e = cudaGetLastError();
+  // Programmatic stream serialisation: this grid's prologue (barrier setup, tensor-memory allocation,
+  // descriptor fetch) may overlap the tail of the previous kernel in the stream.  The kernel touches no
+  // global memory before griddepcontrol.wait, so nothing else changes for the caller.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(Cfg::THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, decode_kernel<Cfg>, tw, tx, p);
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
@@ -219,7 +249,7 @@ struct Fp8WsLayout {
 };
 Fp8WsLayout fp8_ws_layout(int M, int K) {
   Fp8WsLayout w{};
-  w.row_scale_off = STATUS_BYTES;
+  w.row_scale_off = STATUS_BYTES + COUNTER_BYTES;  // behind the tile-counter region, which must stay zero
   w.xq_off = align_up(w.row_scale_off + (size_t)M * 4, 1024);
   w.total = w.xq_off + (size_t)M * (size_t)K;
   return w;
@@ -260,8 +290,17 @@ int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, cons
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int max_pairs = sms / 2;
   const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  fp8_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ta, tw, ty, p);
-  e = cudaGetLastError();
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3((unsigned)(2 * pairs));
+  lc.blockDim = dim3(Cfg::THREADS);
+  lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // prologue overlaps the quantisation kernel's tail
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, fp8_pair_kernel<Cfg>, ta, tw, ty, p);
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
@@ -360,7 +399,12 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   }
 
   // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
-  if (variant == RL_VARIANT_AUTO) variant = (M > 128) ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_TS_N192;
+  if (variant == RL_VARIANT_AUTO) {
+    // with a workspace the pair kernel takes 1/rms from the (overlapped) row-statistics pass; without one it
+    // accumulates the sums of squares itself
+    variant = (M > 128) ? (workspace ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_N256)
+                        : RL_VARIANT_PREFILL_TS_N192;
+  }
 #define RL_PREFILL(BN, ST, AM, TG) \
   launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
   switch (variant) {

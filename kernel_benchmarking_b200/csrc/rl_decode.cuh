@@ -69,6 +69,26 @@ __host__ __device__ __forceinline__ int sk_cta_of_unit(int u, int total, int G) 
   return (u < cut) ? u / (q + 1) : rem + (u - cut) / q;
 }
 
+// A CTA's contiguous run of units, cut at channel-tile boundaries, gives its segments.  They are
+// processed rotated by one - last segment first - so that the partial tiles at both ends of the run
+// (the ones shared with other CTAs) are done early and their cross-CTA fix-up hides
+// behind the whole tiles in the middle; the kernel then ends on a tile it owns alone.
+struct DecodeSegments {
+  int u_begin, u_end, KB, first_tile, nseg;
+  __device__ __forceinline__ DecodeSegments(int b, int e, int kb) : u_begin(b), u_end(e), KB(kb) {
+    first_tile = b / kb;
+    nseg = (e - 1) / kb - first_tile + 1;
+  }
+  // i-th segment in processing order -> natural index, channel tile, first k-block, unit count
+  __device__ __forceinline__ void get(int i, int& nat, int& tile, int& kb0, int& n_units) const {
+    nat = (nseg >= 2) ? (i == 0 ? nseg - 1 : i - 1) : i;
+    tile = first_tile + nat;
+    const int s = max(u_begin, tile * KB), e = min(u_end, (tile + 1) * KB);
+    kb0 = s - tile * KB;
+    n_units = e - s;
+  }
+};
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -97,6 +117,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   const int u_begin = sk_begin(cta, p.units_total, G);
   const int u_end = sk_begin(cta + 1, p.units_total, G);
   const bool has_gamma = (p.gamma != nullptr);
+  const DecodeSegments segs(u_begin, u_end, KB);
+
+  // one unit's loads: W tile (streamed once: evict-first), x tile (re-read by every CTA: evict-last), gamma slice
+  auto issue_unit = [&](int s, int tile, int kb, uint64_t pol_w, uint64_t pol_x) {
+    const int kvalid = min(64, p.K - kb * 64);
+    const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
+    mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
+    tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
+    tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
+    if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+  };
+  const int n_pre = min(STAGES, u_end - u_begin);  // units whose loads go out before the CTA-wide sync
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -114,37 +146,46 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     fence_mbar_init();
     prefetch_tmap(&tm_w);
     prefetch_tmap(&tm_x);
+    launch_dependents();
+    grid_dependency_wait();
+    // fill the ring right away: the first loads need neither tensor memory nor the other warps
+    const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+    int issued = 0;
+    for (int i = 0; i < segs.nseg && issued < n_pre; ++i) {
+      int nat, tile, kb0, n_units;
+      segs.get(i, nat, tile, kb0, n_units);
+      for (int k = 0; k < n_units && issued < n_pre; ++k, ++issued) issue_unit(issued, tile, kb0 + k, pol_w, pol_x);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  grid_dependency_wait();  // every thread: nothing below may touch global memory before the previous grid is done
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (units after the pre-filled ones)
     {
-      const uint64_t pol_w = l2_policy_evict_first();  // W is streamed exactly once
-      const uint64_t pol_x = l2_policy_evict_last();   // x is re-read by every CTA
-      int s = 0;
-      uint32_t ph = 0;
-      int tile = u_begin / KB, kb = u_begin - tile * KB;
-      for (int u = u_begin; u < u_end; ++u) {
-        if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, u)) break;
-        if (elect_one()) {
-          const int kvalid = min(64, p.K - kb * 64);
-          const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
-          mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
-          tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
-          tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
-          if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      int s = (n_pre == STAGES) ? 0 : n_pre;
+      uint32_t ph = (n_pre == STAGES) ? 1u : 0u;
+      int j = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < segs.nseg; ++i) {
+        int nat, tile, kb0, n_units;
+        segs.get(i, nat, tile, kb0, n_units);
+        for (int k = 0; k < n_units; ++k, ++j) {
+          if (j < n_pre) continue;  // went out before the CTA-wide sync
+          if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, j)) { ok = false; break; }
+          if (elect_one()) issue_unit(s, tile, kb0 + k, pol_w, pol_x);
+          __syncwarp();
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        __syncwarp();
-        if (++s == STAGES) { s = 0; ph ^= 1; }
-        if (++kb == KB) { kb = 0; ++tile; }
       }
     }
   } else if (warp == 1) {
@@ -154,10 +195,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      int seg = 0;
-      for (int u = u_begin; ok && u < u_end; ++seg) {
-        const int tile = u / KB, kb0 = u - tile * KB;
-        const int n_units = min(KB - kb0, u_end - u);
+      int u = 0;  // running unit count (for error records only)
+      for (int seg = 0; ok && seg < segs.nseg; ++seg) {
+        int nat, tile, kb0, n_units;
+        segs.get(seg, nat, tile, kb0, n_units);
         const int acc = seg & 1;
         const uint32_t aph = (seg >> 1) & 1;
         if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1, ctl, 1, 3 * STAGES + 2 + acc, seg)) break;
@@ -189,16 +230,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     const int tw = warp - 2;     // 0..3
     const int c = lane & 7;      // 16-byte chunk within the 128-byte row
     bool ok = true;
-    int seg = 0;
-    for (int u = u_begin; ok && u < u_end; ++seg) {
-      const int tile = u / KB, kb0 = u - tile * KB;
-      const int n_units = min(KB - kb0, u_end - u);
+    int u = 0;  // running unit count of the CTA = ring position of the segment's first unit
+    for (int seg = 0; ok && seg < segs.nseg; ++seg) {
+      int nat, tile, kb0, n_units;
+      segs.get(seg, nat, tile, kb0, n_units);
       const int acc = seg & 1;
       const uint32_t aph = (seg >> 1) & 1;
       float ss[NCH];
 #pragma unroll
       for (int i = 0; i < NCH; ++i) ss[i] = 0.f;
-      const int j0 = u - u_begin;  // running unit index of the CTA = ring position
+      const int j0 = u;
       for (int i = ((tw - j0) % 4 + 4) % 4; i < n_units; i += 4) {
         const int j = j0 + i;
         const int s = j % STAGES;
@@ -263,10 +304,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     const int n_local = q * 32 + lane;
     const int epi_tid = threadIdx.x - 192;
     const float inv_k = 1.0f / (float)p.K;
-    int seg = 0;
-    for (int u = u_begin; u < u_end; ++seg) {
-      const int tile = u / KB, kb0 = u - tile * KB;
-      const int n_units = min(KB - kb0, u_end - u);
+    for (int seg = 0; seg < segs.nseg; ++seg) {
+      int nat, tile, kb0, n_units;
+      segs.get(seg, nat, tile, kb0, n_units);
       const int acc = seg & 1;
       const uint32_t aph = (seg >> 1) & 1;
       mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, seg) &&
@@ -300,7 +340,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         if (epi_tid < MPAD) rvec[epi_tid] = 1.0f / sqrtf(tot * inv_k + p.eps);
         named_bar_sync(1, 128);
       } else {
-        const int slot = (seg == 0) ? 0 : 1;
+        const int slot = (nat == 0) ? 0 : 1;  // slot 0: the tile this CTA's run starts in
         float* part = p.partials + (size_t)(cta * 2 + slot) * MPAD * 128;
 #pragma unroll
         for (int m = 0; m < MPAD; ++m) part[m * 128 + n_local] = a[m];
@@ -348,7 +388,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty(acc));
-      u += n_units;
     }
   }
 

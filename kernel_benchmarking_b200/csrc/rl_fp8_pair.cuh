@@ -48,6 +48,7 @@ __device__ __forceinline__ float block_reduce_128(float v, bool is_max, float* s
 
 __global__ void __launch_bounds__(128) rowquant_kernel(const RowQuantParams p) {
   __shared__ float scratch[4];
+  launch_dependents();  // lets the GEMM behind this kernel run its prologue; it waits before its first load
   const int m = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx);
   const uint4* gr = reinterpret_cast<const uint4*>(p.gamma);
@@ -180,6 +181,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     uint32_t ph = 0;
     bool ok = true;
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
+    grid_dependency_wait();  // the quantised activations come from the kernel launched just before
     for (int t = pair; ok && t < total_tiles; t += n_pairs) {
       int mt, nt;
       prefill_tile_coords(t, tp, mt, nt);
@@ -238,6 +240,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const uint32_t swz = (uint32_t)(row & 7);
     const int epi_tid = threadIdx.x - 64;
     const uint32_t lead_tempty0 = mapa_shared(bar_tempty(0), 0);
+    const uint64_t pol_y = l2_policy_evict_first();
     bool ok = true;
     int it = 0;
     uint32_t chunk_no = 0;
@@ -252,6 +255,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         wsc[acc * 256 + epi_tid] = (n < p.N) ? __ldg(p.w_scale + n) : 0.f;
         wsc[acc * 256 + 128 + epi_tid] = (n + 128 < p.N) ? __ldg(p.w_scale + n + 128) : 0.f;
       }
+      grid_dependency_wait();
       const int m = mt * 256 + (int)rank * 128 + row;
       const float rsc = (m < p.M) ? __ldg(p.row_scale + m) : 0.f;
       mbar_wait(bar_tfull(acc), aph, ctl, 3, 2 * STAGES + acc, it);
@@ -301,7 +305,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         named_bar_sync(2, 128);
         if (epi_tid == 0) {
           const int n0 = nt * BN + c * 64;
-          if (n0 < p.N) tma_store_2d(&tm_y, smem_u32(stage), n0, mt * 256 + (int)rank * 128);
+          if (n0 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage), n0, mt * 256 + (int)rank * 128, pol_y);
           tma_store_commit();
         }
       }

@@ -37,6 +37,7 @@ struct PrefillParams {
 // recompute the same sums of squares (N/256 times per row).
 __global__ void __launch_bounds__(128) rowstats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ rstd,
                                                        int M, int K, long long ldx, float eps) {
+  launch_dependents();  // the GEMM behind this kernel may start loading tiles; it waits before it reads rstd
   const int m = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (m >= M) return;

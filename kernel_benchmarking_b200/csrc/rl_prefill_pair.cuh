@@ -305,6 +305,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t swz = (uint32_t)(row & 7);
     const int epi_tid = threadIdx.x - (64 + 128 * TG);
     const uint32_t lead_tempty0 = mapa_shared(bar_tempty(0), 0);
+    const uint64_t pol_y = l2_policy_evict_first();
     bool ok = true;
     int it = 0;
     uint32_t chunk_no = 0;
@@ -315,6 +316,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
       float r_pre = 0.f;
       if (PRESTATS) {
+        // launched with programmatic stream serialisation right behind rowstats_kernel: everything up to
+        // here overlapped it; its results are needed (and guaranteed visible) only from this point on
+        grid_dependency_wait();
         const int m = mt * 256 + (int)rank * 128 + row;
         r_pre = (m < p.M) ? __ldg(p.row_rstd + m) : 0.f;
       }
@@ -337,46 +341,99 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_rsfree(acc));
       }
-#pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c, ++chunk_no) {
-        uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;
-        if (epi_tid == 0) tma_store_wait_read<1>();
+      // convert 32 accumulator columns to bf16: 16 packed words
+      auto cvt32 = [&](const uint32_t (&v)[32], uint32_t (&o)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          o[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * r, __uint_as_float(v[2 * j + 1]) * r);
+      };
+      // write 64 columns (two 16-word halves) of this thread's row into a swizzled staging tile
+      auto sts64 = [&](uint8_t* stage, const uint32_t (&lo)[16], const uint32_t (&hi)[16]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)j ^ swz) << 4)) =
+              make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)(4 + j) ^ swz) << 4)) =
+              make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+        }
+      };
+      const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if constexpr (NACC == 1 && BN == 256) {
+        // One accumulator: the next tile's first MMA waits for this drain, so tensor memory is emptied as
+        // fast as possible - columns 0..127 straight into the two staging tiles, columns 128..255 into
+        // registers as packed bf16 - and released before any store is issued.
+        uint8_t* stage0 = smem + Cfg::OFF_EPI;
+        uint8_t* stage1 = smem + Cfg::OFF_EPI + Cfg::EPI_BYTES;
+        if (epi_tid == 0) tma_store_wait_read<0>();  // the previous tile's stores are done reading the staging tiles
         named_bar_sync(1, 128);
-        uint32_t v0[32], v1[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 64, v0);
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 64 + 32, v1);
-        tmem_wait_ld();
-        if (c == BN / 64 - 1) {
-          // accumulator drained into registers: the pair's MMA warp may start on it again
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
-          if (epi_tid == 0) RL_STAMP(7, it);
-        }
+        uint32_t pk[4][16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(v0[8 * j + 0]) * r, __uint_as_float(v0[8 * j + 1]) * r);
-          o.y = pack_bf16x2(__uint_as_float(v0[8 * j + 2]) * r, __uint_as_float(v0[8 * j + 3]) * r);
-          o.z = pack_bf16x2(__uint_as_float(v0[8 * j + 4]) * r, __uint_as_float(v0[8 * j + 5]) * r);
-          o.w = pack_bf16x2(__uint_as_float(v0[8 * j + 6]) * r, __uint_as_float(v0[8 * j + 7]) * r);
-          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)j ^ swz) << 4)) = o;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v0[32], v1[32];
+          tmem_ld32(trow + c * 64, v0);
+          tmem_ld32(trow + c * 64 + 32, v1);
+          tmem_wait_ld();
+          if (c < 2) {
+            uint32_t lo[16], hi[16];
+            cvt32(v0, lo);
+            cvt32(v1, hi);
+            sts64(c == 0 ? stage0 : stage1, lo, hi);
+          } else {
+            cvt32(v0, pk[2 * (c - 2)]);
+            cvt32(v1, pk[2 * (c - 2) + 1]);
+          }
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(v1[8 * j + 0]) * r, __uint_as_float(v1[8 * j + 1]) * r);
-          o.y = pack_bf16x2(__uint_as_float(v1[8 * j + 2]) * r, __uint_as_float(v1[8 * j + 3]) * r);
-          o.z = pack_bf16x2(__uint_as_float(v1[8 * j + 4]) * r, __uint_as_float(v1[8 * j + 5]) * r);
-          o.w = pack_bf16x2(__uint_as_float(v1[8 * j + 6]) * r, __uint_as_float(v1[8 * j + 7]) * r);
-          *reinterpret_cast<uint4*>(stage + row * 128 + (((uint32_t)(4 + j) ^ swz) << 4)) = o;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+        if (epi_tid == 0) RL_STAMP(7, it);
+        fence_proxy_async_smem();
+        named_bar_sync(2, 128);
+        const int m0 = mt * 256 + (int)rank * 128;
+        if (epi_tid == 0) {
+          if (nt * BN < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage0), nt * BN, m0, pol_y);
+          if (nt * BN + 64 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage1), nt * BN + 64, m0, pol_y);
+          tma_store_commit();
+          tma_store_wait_read<0>();
         }
+        named_bar_sync(1, 128);
+        sts64(stage0, pk[0], pk[1]);
+        sts64(stage1, pk[2], pk[3]);
         fence_proxy_async_smem();
         named_bar_sync(2, 128);
         if (epi_tid == 0) {
-          const int n0 = nt * BN + c * 64;
-          if (n0 < p.N) tma_store_2d(&tm_y, smem_u32(stage), n0, mt * 256 + (int)rank * 128);
+          if (nt * BN + 128 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage0), nt * BN + 128, m0, pol_y);
+          if (nt * BN + 192 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage1), nt * BN + 192, m0, pol_y);
           tma_store_commit();
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c, ++chunk_no) {
+          uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;
+          if (epi_tid == 0) tma_store_wait_read<1>();
+          named_bar_sync(1, 128);
+          uint32_t v0[32], v1[32];
+          tmem_ld32(trow + c * 64, v0);
+          tmem_ld32(trow + c * 64 + 32, v1);
+          tmem_wait_ld();
+          if (c == BN / 64 - 1) {
+            // accumulator drained into registers: the pair's MMA warp may start on it again
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+            if (epi_tid == 0) RL_STAMP(7, it);
+          }
+          uint32_t lo[16], hi[16];
+          cvt32(v0, lo);
+          cvt32(v1, hi);
+          sts64(stage, lo, hi);
+          fence_proxy_async_smem();
+          named_bar_sync(2, 128);
+          if (epi_tid == 0) {
+            const int n0 = nt * BN + c * 64;
+            if (n0 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage), n0, mt * 256 + (int)rank * 128, pol_y);
+            tma_store_commit();
+          }
         }
       }
     }

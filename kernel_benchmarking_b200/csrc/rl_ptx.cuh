@@ -121,6 +121,15 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// launch_dependents: the next kernel in the stream (if it was launched with programmatic stream
+// serialisation) may start its prologue once every CTA of this grid has got here or exited.
+// grid_dependency_wait: returns once all grids this one depends on have completed and their memory
+// is visible; a no-op for a normally launched kernel.  Nothing that another kernel may have written
+// or may still read is touched before it.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
@@ -161,6 +170,13 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
                "r"(x), "r"(y)
+               : "memory");
+}
+// Store with an L2 eviction-priority hint: y is written once and not read again by these kernels, so
+// it should not push the operands (which every column tile re-reads) out of L2.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, uint32_t src, int x, int y, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(map),
+               "r"(src), "r"(x), "r"(y), "l"(policy)
                : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

@@ -42,7 +42,7 @@ def test_version_and_error_strings(lib):
 
 def test_workspace_bytes_is_pure_arithmetic(lib):
     small = lib.rl_workspace_bytes(4096, 6144, 4096, 0)
-    assert small == 256 + 4096 * 4          # status block + one 1/rms per token
+    assert small == 256 + 65536 + 4096 * 4  # status block + tile-counter region + one 1/rms per token
     w16 = lib.rl_workspace_bytes(16, 28672, 4096, 0)
     w1 = lib.rl_workspace_bytes(1, 28672, 4096, 0)
     w64 = lib.rl_workspace_bytes(64, 28672, 4096, 0)

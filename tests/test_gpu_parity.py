@@ -297,3 +297,20 @@ def test_fp8_bad_arguments():
         kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), Wq.to(DEV), 1e-6)                 # scales missing
     with pytest.raises(ValueError):
         kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, w_scale=w_scale.to(DEV))  # scales with bf16 W
+
+
+def test_host_buffer_front_end():
+    """Pinned host in, pinned host out, several steps in flight; results equal the direct call."""
+    M, N, K = 300, 520, 320
+    x, gm, W = orc.make_inputs(M, N, K, seed=21)
+    op = kb.HostRMSNormLinear(gm.to(DEV), W.to(DEV), 1e-6, max_tokens=M, depth=2)
+    xs = [(x * (i + 1)).pin_memory() for i in range(5)]
+    ys = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    for xh, yh in zip(xs, ys):
+        op.submit(xh, yh)
+    op.wait()
+    kb.check_status()
+    for xh, yh in zip(xs, ys):
+        assert orc.rel_max_err(yh, orc.reference_fp32(xh, gm, W, 1e-6)) <= BF16_TOL
+    with pytest.raises(ValueError):
+        op.submit(x, ys[0])          # not pinned
