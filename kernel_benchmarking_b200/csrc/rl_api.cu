@@ -42,8 +42,33 @@ EncodeTiledFn encode_tiled() {
 }
 
 // Row-major 2-D tensor [outer, inner] of 1- or 2-byte elements, 128-byte-swizzled boxes.
+// Encoding a descriptor costs a few microseconds of host time, which shows at decode sizes (a 40 us
+// kernel): the last few descriptors are kept per host thread, keyed by everything that defines them.
+struct MapKey {
+  const void* ptr;
+  uint64_t inner, outer, stride;
+  uint32_t box_inner, box_outer;
+  int dt, dev;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+           box_outer == o.box_outer && dt == o.dt && dev == o.dev;
+  }
+};
 int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, uint64_t inner,
              uint64_t outer, uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
+  constexpr int SLOTS = 16;
+  thread_local MapKey keys[SLOTS];
+  thread_local CUtensorMap maps[SLOTS];
+  thread_local bool used[SLOTS] = {false};
+  thread_local int next = 0;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  const MapKey key{ptr, inner, outer, row_stride_elems, box_inner, box_outer, (int)dt, dev};
+  for (int i = 0; i < SLOTS; ++i)
+    if (used[i] && keys[i] == key) {
+      *map = maps[i];
+      return RL_OK;
+    }
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return RL_ERR_TENSOR_MAP;
   cuuint64_t dims[2] = {inner, outer};
@@ -52,7 +77,32 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const voi
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? RL_OK : RL_ERR_TENSOR_MAP;
+  if (r != CUDA_SUCCESS) return RL_ERR_TENSOR_MAP;
+  keys[next] = key;
+  maps[next] = *map;
+  used[next] = true;
+  next = (next + 1) % SLOTS;
+  return RL_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of on every call.
+template <class KernelFn>
+cudaError_t set_smem_once(KernelFn fn, int bytes) {
+  // keyed by the kernel's address: every instantiation with the same signature shares this function
+  static std::mutex mu;
+  static const void* seen[64][64];
+  static int n_seen[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  dev &= 63;
+  const void* key = reinterpret_cast<const void*>(fn);
+  std::lock_guard<std::mutex> lk(mu);
+  for (int i = 0; i < n_seen[dev]; ++i)
+    if (seen[dev][i] == key) return cudaSuccess;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && n_seen[dev] < 64) seen[dev][n_seen[dev]++] = key;
+  return e;
 }
 
 struct DeviceInfo {
@@ -118,8 +168,7 @@ int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, voi
   p.status = status;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  cudaError_t e = cudaFuncSetAttribute(prefill_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::SMEM_BYTES);
+  cudaError_t e = set_smem_once(prefill_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   prefill_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, p);
   e = cudaGetLastError();
@@ -152,8 +201,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
   p.trace = status ? reinterpret_cast<long long*>(reinterpret_cast<uint8_t*>(status) + 4096) : nullptr;
 #endif
-  cudaError_t e = cudaFuncSetAttribute(prefill_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::SMEM_BYTES);
+  cudaError_t e = set_smem_once(prefill_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   // how many CTA pairs the device can hold at once (pairs must sit on neighbouring SMs)
   static int max_pairs_cache[64] = {0};
@@ -222,10 +270,12 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   p.counters = reinterpret_cast<int*>(ws + wl.counters_off);
   p.ssq_partials = reinterpret_cast<float*>(ws + wl.ssq_off);
   p.partials = reinterpret_cast<float*>(ws + wl.partials_off);
+#ifdef RL_TRACE
+  p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
+#endif
   int grid = sms < RL_MAX_CTAS ? sms : RL_MAX_CTAS;
   if (units < grid) grid = (int)units;
-  cudaError_t e = cudaFuncSetAttribute(decode_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::SMEM_BYTES);
+  cudaError_t e = set_smem_once(decode_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   // Programmatic stream serialisation: this grid's prologue (barrier setup, tensor-memory allocation,
   // descriptor fetch) may overlap the tail of the previous kernel in the stream.  The kernel touches no
@@ -284,8 +334,7 @@ int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, cons
   p.n_tiles = (N + 255) / 256;
   p.group_m = 8;
   p.status = status;
-  cudaError_t e = cudaFuncSetAttribute(fp8_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::SMEM_BYTES);
+  cudaError_t e = set_smem_once(fp8_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int max_pairs = sms / 2;
