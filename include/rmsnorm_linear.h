@@ -130,6 +130,13 @@ int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void*
                                    int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
                                    float eps, void* stream);
 
+/* Plain bf16 GEMM C[M, N] = A[M, K] . B[N, K]^T (fp32 accumulation) on the same CTA-pair machinery with
+ * the norm switched off: the "max" line the reference times beside every fused kernel
+ * (`torch_gemm`, demo/new_profiling/rmsnorm_linear_new.py:29-31; native form
+ * third_party/cublas_gemm/python/ext_kernel.cu:30-53).  `workspace` (>= 256 bytes) may be NULL. */
+int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                 int64_t lda, int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Read the status block of a workspace (synchronises the stream's device: use
  * outside the hot loop).  Returns RL_OK or RL_ERR_DEVICE_TIMEOUT; when `detail`
  * is not NULL it receives 8 ints: code, role, barrier, block, index, parity, 0, 0.

@@ -177,7 +177,8 @@ int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, voi
 
 template <class Cfg>
 int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
-                        int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st) {
+                        int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st,
+                        bool no_norm = false) {
   CUtensorMap tx, tw, ty;
   int rc;
   if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
@@ -191,7 +192,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.n_tiles = (N + Cfg::BN - 1) / Cfg::BN;
   p.group_m = 8;
   p.status = status;
-  if (Cfg::PRESTATS) {
+  if (Cfg::PRESTATS && !no_norm) {
     if (status == nullptr) return RL_ERR_WORKSPACE;
     float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + STATUS_BYTES + COUNTER_BYTES);
     rowstats_kernel<<<(M + 3) / 4, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), rstd, M, K, ldx, eps);
@@ -537,6 +538,22 @@ int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void*
   if (e != cudaSuccess) return cuda_err(e);
   return launch_decode<DecodeCfg<16, 12>>(x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw,
                                           ldy, eps, scratch, wl, di.sms, st);
+}
+
+int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!A || !B || !C) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < K || ldc < N) return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || !aligned16(A) || !aligned16(B) || !aligned16(C))
+    return RL_ERR_ALIGNMENT;
+  if (workspace && workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
+      A, nullptr, B, C, M, N, K, lda, ldb, ldc, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
+      /*no_norm=*/true);
 }
 
 int rl_read_status(const void* workspace, int* detail) {

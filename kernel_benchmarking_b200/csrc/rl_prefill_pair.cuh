@@ -246,7 +246,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (q == 0 && lane == 0) RL_STAMP(3, j);
-        if (RL_DEBUG(1)) {  // experiment: no tile work at all
+        if ((!TS && PRESTATS) || RL_DEBUG(1)) {  // nothing to fold and nothing to sum: just hand the slot on
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(lead_ready0 + 8u * s);
           continue;
@@ -320,7 +320,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         // here overlapped it; its results are needed (and guaranteed visible) only from this point on
         grid_dependency_wait();
         const int m = mt * 256 + (int)rank * 128 + row;
-        r_pre = (m < p.M) ? __ldg(p.row_rstd + m) : 0.f;
+        r_pre = (p.row_rstd == nullptr) ? 1.0f : ((m < p.M) ? __ldg(p.row_rstd + m) : 0.f);
       }
       mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, it) &&
           (PRESTATS || mbar_wait(bar_rsfull(acc), aph, ctl, 3, 3 * STAGES + 2 * NACC + acc, it));

@@ -132,6 +132,32 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
     return out
 
 
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K] @ b [N, K].t() in bf16 with fp32 accumulation, no norm: the reference's "max" line
+    (`torch_gemm`, demo/new_profiling/rmsnorm_linear_new.py:29-31) on this library's CTA-pair kernel."""
+    _check_matrix("a", a, torch.bfloat16)
+    _check_matrix("b", b, torch.bfloat16)
+    M, K = a.shape
+    N, K2 = b.shape
+    if K2 != K or b.device != a.device:
+        raise ValueError("a [M, K] and b [N, K] must share K and the device")
+    if out is None:
+        ldc = (N + 7) // 8 * 8
+        buf = torch.empty((M, ldc), dtype=torch.bfloat16, device=a.device)
+        out = buf if ldc == N else buf[:, :N]
+    else:
+        _check_matrix("out", out, torch.bfloat16)
+    if M == 0 or N == 0:
+        return out
+    stream = _stream_ptr(a.device)
+    with _on_device(a.device):
+        ws = _workspace(a.device, 256, stream)
+        rc = _lib.load().rl_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                      out.stride(0), ws.data_ptr(), ws.numel(), stream)
+    _lib.check(rc, "rl_gemm_bf16")
+    return out
+
+
 def quantize_rows_e4m3(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float = 1e-6):
     """First kernel of the FP8 path on its own: returns (q [M, K] float8_e4m3fn, row_scale [M] fp32) with
     q = e4m3(x * gamma * 448 / amax_row) and row_scale = rsqrt(mean x^2 + eps) * amax_row / 448."""

@@ -314,3 +314,27 @@ def test_host_buffer_front_end():
         assert orc.rel_max_err(yh, orc.reference_fp32(xh, gm, W, 1e-6)) <= BF16_TOL
     with pytest.raises(ValueError):
         op.submit(x, ys[0])          # not pinned
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 320), (2048, 2048, 2048), (4096, 1024, 4096)])
+def test_plain_gemm_max_line(M, N, K):
+    """The norm-free GEMM (the reference's "max" line) against fp32 matmul."""
+    x, _, W = orc.make_inputs(M, N, K, seed=M + K)
+    y = kb.gemm_nt(x.to(DEV), W.to(DEV))
+    torch.cuda.synchronize()
+    kb.check_status()
+    ref = x.float() @ W.float().t()
+    assert orc.rel_max_err(y.cpu(), ref) <= BF16_TOL
+
+
+def test_harness_job_runs_and_reports(tmp_path):
+    """The reference-style job on its smallest shape: rows for b200 / torch / max, accuracy columns filled."""
+    from kernel_benchmarking_b200 import harness
+    job = harness.rmsnorm_linear_job(0)
+    rows = job.run(pause_s=0.0)
+    by = {r.label.split(":")[-1]: r for r in rows}
+    assert set(by) == {"b200", "torch", "max", "max_b200"}
+    assert by["b200"].rmse is not None and by["b200"].rmse <= 2.0 * by["torch"].rmse + 1e-3
+    assert by["b200"].ms_median > 0 and by["b200"].baseline_speedup > 0
+    harness.write_rows(rows, str(tmp_path / "r.csv"))
+    assert (tmp_path / "r.csv").read_text().startswith("rmsnorm_linear:0:b200,2048,2048,2048,")

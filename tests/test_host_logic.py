@@ -96,3 +96,31 @@ def test_wrong_shard_size_is_rejected():
     W = torch.zeros(10, 16)
     with pytest.raises(ValueError, match="rows of W"):
         ColumnParallelRMSNormLinear(W, None, 1e-6, 64, local_fn=lambda *a: None)
+
+
+def test_harness_csv_contract(tmp_path):
+    """Rows concatenate with the reference's CSVs: same columns, same order, appended."""
+    from kernel_benchmarking_b200 import harness
+    assert harness.ExperimentRow.header() == ("label,m,n,k,ms_median,ms_mean,ms_std,max_abs,max_rel,rmse,"
+                                              "baseline_speedup,metadata,autotune_seconds")
+    row = harness.ExperimentRow("rmsnorm_linear:1:b200", 4096, 4096, 4096, ms_median=0.1, ms_mean=0.11, ms_std=0.01)
+    assert row.csv().startswith("rmsnorm_linear:1:b200,4096,4096,4096,0.1,0.11,0.01,None")
+    p = tmp_path / "out.csv"
+    harness.write_rows([row], str(p))
+    harness.write_rows([row], str(p))
+    assert p.read_text().count("\n") == 2
+    assert len(harness.RMSNORM_LINEAR_SHAPES) == 10 and harness.RMSNORM_LINEAR_SHAPES[1] == (4096, 4096, 4096)
+    with pytest.raises(IndexError):
+        harness.rmsnorm_linear_job(10)       # the reference's run script walks off the table at index 10 too
+
+
+def test_harness_metrics_and_distribution():
+    from kernel_benchmarking_b200 import harness
+    ref = torch.tensor([[1.0, -2.0], [0.5, 4.0]])
+    out = torch.tensor([[1.5, -2.0], [0.5, 3.0]])
+    assert abs(harness.rmse(ref, out) - (1.25 / 4) ** 0.5) < 1e-12
+    max_abs, max_rel = harness.max_errors(ref, out)
+    assert max_abs == 1.0 and abs(max_rel - 0.5) < 1e-7     # 0.5 / max(|1|, 1) vs 1 / 4
+    g = torch.Generator().manual_seed(1)
+    t = harness.normal_bernoulli((2000, 500), generator=g)
+    assert 0.9 < float(t.std()) < 1.2 and float(t.abs().max()) > 8.0
