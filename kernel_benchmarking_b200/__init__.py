@@ -5,6 +5,6 @@ dungwoong/kernel-benchmarking profiles (demo/rmsnorm_linear.py).  There is no CP
 or PyTorch fallback: the compiled library must be present.
 """
 from .host import HostRMSNormLinear  # noqa: F401
-from .ops import check_status, gemm_nt, quantize_rows_e4m3, rmsnorm_linear  # noqa: F401
+from .ops import check_status, gemm_nt, quantize_rows_e4m3, rmsnorm_linear, rmsnorm_swiglu  # noqa: F401
 
-__all__ = ["rmsnorm_linear", "quantize_rows_e4m3", "check_status", "HostRMSNormLinear", "gemm_nt"]
+__all__ = ["rmsnorm_linear", "quantize_rows_e4m3", "check_status", "HostRMSNormLinear", "gemm_nt", "rmsnorm_swiglu"]

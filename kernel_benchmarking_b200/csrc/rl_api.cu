@@ -182,14 +182,16 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   CUtensorMap tx, tw, ty;
   int rc;
   if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
-  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, N, ldw, 64, Cfg::BN / 2))) return rc;
+  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, ldw, 64,
+                     Cfg::BN / 2)))
+    return rc;
   if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
   if (Cfg::AMODE == A_SS_DIRECT && gamma != nullptr) return RL_ERR_BAD_VARIANT;
   PrefillParams p{};
   p.M = M; p.N = N; p.K = K; p.eps = eps;
   p.gamma = gamma;
   p.m_tiles = (M + 255) / 256;
-  p.n_tiles = (N + Cfg::BN - 1) / Cfg::BN;
+  p.n_tiles = Cfg::SWIGLU ? (N + 127) / 128 : (N + Cfg::BN - 1) / Cfg::BN;  // SwiGLU: N = output channels, W has 2N rows
   p.group_m = 8;
   p.status = status;
   if (Cfg::PRESTATS && !no_norm) {
@@ -538,6 +540,26 @@ int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void*
   if (e != cudaSuccess) return cuda_err(e);
   return launch_decode<DecodeCfg<16, 12>>(x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw,
                                           ldy, eps, scratch, wl, di.sms, st);
+}
+
+int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void* y, int M, int N, int K, int64_t ldx,
+                           int64_t ldw, int64_t ldy, float eps, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (!x || !W || !y) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return RL_ERR_BAD_SHAPE;
+  // a tile pairs 128 gate rows with 128 up rows: N a multiple of 128 keeps a tile from straddling the two halves
+  if ((K & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7) || (N & 127) || !aligned16(x) || !aligned16(W) || !aligned16(y) ||
+      (gamma && !aligned16(gamma)))
+    return RL_ERR_ALIGNMENT;
+  const size_t need = ws_layout(65 > M ? 65 : M, N).total;
+  if (!workspace || workspace_bytes < need) return RL_ERR_WORKSPACE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  return launch_prefill_pair<PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>>(
+      x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw, ldy, eps,
+      reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream);
 }
 
 int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,

@@ -47,11 +47,16 @@ namespace rl {
 #define RL_DEBUG(bit) false
 #endif
 
-template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false>
+template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false, bool SWIGLU_ = false>
 struct PairCfg {
   static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_, ASLOTS = ASLOTS_, TG = TG_, AMODE = AMODE_;
   // PRESTATS: 1/rms per token comes from rowstats_kernel; the transform warps only fold gamma
   static constexpr bool PRESTATS = PRESTATS_;
+  // SWIGLU: W is [2 n, K] = gate rows then up rows (python/baselines/rmsnorm_swiglu.py:36-42).  The rank-0 CTA
+  // loads gate channels, the rank-1 CTA the matching up channels, so accumulator columns [0,128) and
+  // [128,256) hold gate and up of the same 128 output channels and the epilogue emits silu(gate) * up.
+  static constexpr bool SWIGLU = SWIGLU_;
+  static_assert(!SWIGLU_ || (BN_ == 256 && NACC_ == 1), "SwiGLU epilogue: 256-column tile, one accumulator");
   static constexpr int THREADS = 64 + 128 * TG + 128;
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the W tile
@@ -87,6 +92,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   constexpr int BN = Cfg::BN, NACC = Cfg::NACC, STAGES = Cfg::STAGES, ASLOTS = Cfg::ASLOTS, TG = Cfg::TG;
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
   constexpr bool PRESTATS = Cfg::PRESTATS;
+  constexpr bool SWIGLU = Cfg::SWIGLU;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
@@ -166,7 +172,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           const uint32_t lead_ready = lead_ready0 + 8u * s;
           mbar_expect_tx_cluster(lead_ready, Cfg::B_BYTES);
           tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kb * 64,
-                           nt * BN + (int)rank * (BN / 2));
+                           SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
         }
         __syncwarp();
         ++jp;
@@ -358,7 +364,45 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
       };
       const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      if constexpr (NACC == 1 && BN == 256) {
+      if constexpr (SWIGLU) {
+        // p.N = n output channels; this tile covers channels nt*128 .. +127: gate in columns [0,128), up in [128,256)
+        uint8_t* stage0 = smem + Cfg::OFF_EPI;
+        uint8_t* stage1 = smem + Cfg::OFF_EPI + Cfg::EPI_BYTES;
+        if (epi_tid == 0) tma_store_wait_read<0>();
+        named_bar_sync(1, 128);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t lo[16], hi[16];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t vg[32], vu[32];
+            tmem_ld32(trow + c * 64 + h * 32, vg);
+            tmem_ld32(trow + 128 + c * 64 + h * 32, vu);
+            tmem_wait_ld();
+            uint32_t (&o)[16] = (h == 0) ? lo : hi;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(vg[2 * j]) * r, g1 = __uint_as_float(vg[2 * j + 1]) * r;
+              const float u0 = __uint_as_float(vu[2 * j]) * r, u1 = __uint_as_float(vu[2 * j + 1]) * r;
+              o[j] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+            }
+          }
+          if (c == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+          }
+          sts64(c == 0 ? stage0 : stage1, lo, hi);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(2, 128);
+        if (epi_tid == 0) {
+          const int m0 = mt * 256 + (int)rank * 128;
+          if (nt * 128 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage0), nt * 128, m0, pol_y);
+          if (nt * 128 + 64 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage1), nt * 128 + 64, m0, pol_y);
+          tma_store_commit();
+        }
+      } else if constexpr (NACC == 1 && BN == 256) {
         // One accumulator: the next tile's first MMA waits for this drain, so tensor memory is emptied as
         // fast as possible - columns 0..127 straight into the two staging tiles, columns 128..255 into
         // registers as packed bf16 - and released before any store is issued.

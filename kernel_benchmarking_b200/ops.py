@@ -132,6 +132,36 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
     return out
 
 
+def rmsnorm_swiglu(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tensor, eps: float = 1e-6, *,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(h[:, :n]) * h[:, n:] with h = rms_norm(x, weight=gamma) @ W.t(), W [2n, K] (gate rows, then up rows):
+    the reference's `rmsnorm_swiglu(a, bb1, eps)` (python/baselines/rmsnorm_swiglu.py:36-42) in one kernel."""
+    _check_matrix("x", x, torch.bfloat16)
+    _check_matrix("W", W, torch.bfloat16)
+    M, K = x.shape
+    N2, K2 = W.shape
+    if K2 != K or W.device != x.device or N2 % 2:
+        raise ValueError("W must be [2n, K] on x's device")
+    N = N2 // 2
+    if gamma is not None and (not gamma.is_cuda or gamma.dtype != torch.bfloat16 or gamma.shape != (K,)):
+        raise ValueError("gamma must be a bf16 CUDA vector of length K")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        _check_matrix("out", out, torch.bfloat16)
+    if M == 0:
+        return out
+    lib = _lib.load()
+    stream = _stream_ptr(x.device)
+    with _on_device(x.device):
+        ws = _workspace(x.device, lib.rl_workspace_bytes(max(M, 65), N, K, _lib.RL_W_BF16), stream)
+        rc = lib.rl_rmsnorm_swiglu_bf16(x.data_ptr(), None if gamma is None else gamma.data_ptr(), W.data_ptr(),
+                                        out.data_ptr(), M, N, K, x.stride(0), W.stride(0), out.stride(0),
+                                        ctypes.c_float(eps), ws.data_ptr(), ws.numel(), stream)
+    _lib.check(rc, "rl_rmsnorm_swiglu_bf16")
+    return out
+
+
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a [M, K] @ b [N, K].t() in bf16 with fp32 accumulation, no norm: the reference's "max" line
     (`torch_gemm`, demo/new_profiling/rmsnorm_linear_new.py:29-31) on this library's CTA-pair kernel."""

@@ -52,6 +52,15 @@ def torch_rmsnorm_linear_decomposed(a: torch.Tensor, gamma: torch.Tensor | None,
     return n.to(a.dtype) @ b.t()
 
 
+def torch_rmsnorm_swiglu(a: torch.Tensor, gamma: torch.Tensor | None, bb1: torch.Tensor,
+                         eps: float = 1e-5) -> torch.Tensor:
+    """python/baselines/rmsnorm_swiglu.py:36-42 (`rmsnorm_swiglu`) with `swiglu_concat` (:3-10): bb1 is [2n, k];
+    o = rms_norm(a) @ bb1.t(); silu(o[:, :n]) * o[:, n:]."""
+    o = torch_rmsnorm(a, gamma, eps) @ bb1.t()
+    o1, o2 = o.chunk(2, dim=1)
+    return torch.nn.functional.silu(o1) * o2
+
+
 def reference_fp32(x: torch.Tensor, gamma: torch.Tensor | None, W: torch.Tensor, eps: float,
                    w_scale: torch.Tensor | None = None, dtype=torch.float32) -> torch.Tensor:
     """The parity target for the GPU kernels: inputs (bf16 / e4m3 bit patterns as

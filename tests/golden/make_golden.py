@@ -30,6 +30,7 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
 def main(ref_root: str) -> None:
     sys.path.insert(0, os.path.join(ref_root, "python"))
     from baselines.rmsnorm_swiglu import rmsnorm_linear as ref_rmsnorm_linear  # noqa: E402
+    from baselines.rmsnorm_swiglu import rmsnorm_swiglu as ref_rmsnorm_swiglu  # noqa: E402
     from baselines.rmsnorm_swiglu_trt import RMSNormLinearModule  # noqa: E402
 
     torch.manual_seed(18)  # the reference's seed, demo/rmsnorm_linear.py:20
@@ -102,6 +103,15 @@ def main(ref_root: str) -> None:
         x_bits=bf16_bits(x), gamma_bits=bf16_bits(gamma), W_bf16_bits=bf16_bits(W),
         Wq_codes=Wq.view(torch.uint8).numpy(), w_scale=w_scale.numpy(), eps=np.float64(1e-6),
         y_ref_fp64=y64.float().numpy(),
+    )
+    # ---- case 6: fused RMSNorm -> SwiGLU (gate rows then up rows), bf16 inputs, no gamma ----
+    M, n, K = 48, 128, 192
+    x = torch.randn(M, K).to(torch.bfloat16)
+    bb1 = (torch.randn(2 * n, K) * K ** -0.5).to(torch.bfloat16)
+    np.savez_compressed(
+        os.path.join(HERE, "swiglu_bf16_48x128x192.npz"),
+        x_bits=bf16_bits(x), W_bits=bf16_bits(bb1), eps=np.float64(1e-5),
+        y_ref_fp64=ref_rmsnorm_swiglu(x.double(), bb1.double(), 1e-5).float().numpy(),
     )
     print("golden vectors written to", HERE)
 

@@ -338,3 +338,23 @@ def test_harness_job_runs_and_reports(tmp_path):
     assert by["b200"].ms_median > 0 and by["b200"].baseline_speedup > 0
     harness.write_rows(rows, str(tmp_path / "r.csv"))
     assert (tmp_path / "r.csv").read_text().startswith("rmsnorm_linear:0:b200,2048,2048,2048,")
+
+
+def test_swiglu_golden_and_shapes(golden_dir):
+    """Fused RMSNorm -> SwiGLU: the reference's golden vector, then larger shapes with gamma."""
+    g = np.load(os.path.join(golden_dir, "swiglu_bf16_48x128x192.npz"))
+    x, W = bf16(g["x_bits"]), bf16(g["W_bits"])
+    y = kb.rmsnorm_swiglu(x.to(DEV), None, W.to(DEV), float(g["eps"]))
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert orc.rel_max_err(y.cpu(), torch.from_numpy(g["y_ref_fp64"])) <= BF16_TOL
+    for (M, n, K) in [(300, 256, 320), (1024, 1792, 1024), (4096, 2048, 4096)]:
+        x, gm, W = orc.make_inputs(M, 2 * n, K, seed=n)
+        y = kb.rmsnorm_swiglu(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6)
+        torch.cuda.synchronize()
+        kb.check_status()
+        ref = orc.torch_rmsnorm_swiglu(x.float(), gm.float(), W.float(), 1e-6)
+        assert y.shape == (M, n)
+        assert orc.rel_max_err(y.cpu(), ref) <= BF16_TOL
+    with pytest.raises(ValueError):
+        kb.rmsnorm_swiglu(x.to(DEV), gm.to(DEV), W[:200].contiguous().to(DEV), 1e-6)   # n not a multiple of 128

@@ -127,3 +127,16 @@ def test_config1_cpu_plumbing():
     assert orc.rel_max_err(y, y64) < 1e-5
     rmse, max_abs, max_rel = orc.ref_metrics(y64.float(), y)
     assert rmse < 1e-5 and max_abs < 1e-4 and max_rel < 1e-4
+
+
+def test_swiglu_golden(golden_dir):
+    """The RMSNorm -> SwiGLU restatement against the reference's own `rmsnorm_swiglu` output."""
+    g = load(golden_dir, "swiglu_bf16_48x128x192.npz")
+    x, W, eps = bf16(g["x_bits"]), bf16(g["W_bits"]), float(g["eps"])
+    y = orc.torch_rmsnorm_swiglu(x.double(), None, W.double(), eps)
+    np.testing.assert_allclose(y.float().numpy(), g["y_ref_fp64"], rtol=1e-6, atol=1e-6)
+    # numpy restatement: h = rmsnorm(x) @ W^T, silu(gate) * up
+    h = orc.np_rmsnorm_linear(orc.bf16_bits_to_f32(g["x_bits"]), None, orc.bf16_bits_to_f32(g["W_bits"]), eps)
+    n = h.shape[1] // 2
+    y_np = h[:, :n] / (1.0 + np.exp(-h[:, :n])) * h[:, n:]
+    np.testing.assert_allclose(y_np.astype(np.float32), g["y_ref_fp64"], rtol=1e-5, atol=1e-6)
