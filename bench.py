@@ -52,8 +52,8 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "prefill_qkv_4096x6144x4096"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries (profiles/)
 NCU_TRAFFIC_BYTES = {
-    "prefill_qkv_4096x6144x4096": 165.6e6,     # profiles/prefill_pair_kernel_4096x6144x4096_bf16.md
-    "decode_16x28672x4096": 241.0e6,           # profiles/decode_kernel_16x28672x4096_bf16.md
+    "prefill_qkv_4096x6144x4096": 164.4e6,     # profiles/prefill_pair_kernel_4096x6144x4096_bf16.md
+    "decode_16x28672x4096": 240.3e6,           # profiles/decode_kernel_16x28672x4096_bf16.md
     "fp8w_8192x14336x4096": 471.3e6,           # profiles/fp8_pair_kernel_8192x14336x4096_e4m3.md (GEMM kernel only)
 }
 L2_BYTES = 126 * 1024 * 1024
@@ -359,7 +359,8 @@ def main():
                     "ms_per_step": e2e_ms, "note": "HostRMSNormLinear: x from pinned host memory and y back to pinned host "
                     "memory every step, copy-in / kernel / copy-out of consecutive steps overlapped on three streams; "
                     "W and gamma are weights, resident on the device"},
-            "gpu_launches": args.steps * world * (2 if fp8 else 1),
+            # M > 128 and the FP8 path launch two kernels per step (row statistics / quantisation, then the GEMM)
+            "gpu_launches": args.steps * world * (2 if (fp8 or M > 128) else 1),
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peaks['source']}" + (" bf16 x 2 (no FP8 peak was measured)" if fp8 else ""),
                          "algorithmic_bytes": step_bytes, "algorithmic_flops": flops},
