@@ -48,6 +48,9 @@ WORKLOADS = {
     "mlp_shard4_16384x14336x8192": (16384, 14336, 8192, "tensor"),
     "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor"),
     "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor"),   # e4m3 weights + per-channel scales
+    # strong scaling: the weight is split along N over the ranks (N below is the whole layer)
+    "strong_mlp_16384x57344x8192": (16384, 57344, 8192, "tensor"),
+    "strong_fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor"),
 }
 DEFAULT_WORKLOAD = "prefill_qkv_4096x6144x4096"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries (profiles/)
@@ -236,7 +239,12 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     M, N, K, bound = WORKLOADS[args.workload]
-    fp8 = args.workload.startswith("fp8w")
+    strong = args.workload.startswith("strong_")
+    if strong:
+        from kernel_benchmarking_b200.sharding import shard_bounds
+        n0, n1 = shard_bounds(N, world, rank, multiple=256)
+        N = n1 - n0          # this rank's block of output channels
+    fp8 = "fp8w" in args.workload
     step_bytes = algorithmic_bytes(M, N, K, fp8)
     sets = max(2, -(-2 * L2_BYTES // step_bytes))   # rotate enough buffer sets to exceed 2x L2
     bufs = make_buffers(M, N, K, dev, sets, seed=18 + rank, fp8=fp8)
@@ -348,7 +356,7 @@ def main():
             achieved, peak, r_unit = step_bytes / (per_gpu_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
         line = {
             "metric": metric_name(bound), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)" if fp8 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "M": M, "N_per_gpu": N, "K": K, "eps": 1e-6, "gamma": True,
                        "sharding": f"column-parallel x{world}, x replicated, no collective",

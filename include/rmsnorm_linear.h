@@ -145,6 +145,14 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
 int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
                  int64_t lda, int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Self-test of the kernels' failure detection.  Launches one small CTA that waits on a barrier nothing
+ * ever arrives on, with the given limit (<= 1 s); the wait must give up, record RL_ERR_DEVICE_TIMEOUT
+ * in the workspace's status block (role 9) and return, leaving the context usable.  Afterwards
+ * rl_read_status reports the timeout; rl_workspace_init clears it.  No reference counterpart (the
+ * reference has no failure handling; its native code exits on a CUDA error,
+ * third_party/cublas_gemm/cublas_gemm.cu:17-29). */
+int rl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream);
+
 /* Read the status block of a workspace (synchronises the stream's device: use
  * outside the hot loop).  Returns RL_OK or RL_ERR_DEVICE_TIMEOUT; when `detail`
  * is not NULL it receives 8 ints: code, role, barrier, block, index, parity, 0, 0.

@@ -37,8 +37,6 @@ VARIANTS = {
     "prefill_pair_n192": 10,
     "prefill_pair_direct": 11,
     "prefill_pair_prestats": 14,
-    "x12": 12, "x13": 13, "x15": 15,
-    "x6": 6, "x7": 7, "x8": 8,
     "decode": 20,
 }
 
@@ -55,6 +53,7 @@ SYMBOLS = [
     ("rl_rmsnorm_linear_bf16_noalloc", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp]),
     ("rl_rmsnorm_swiglu_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _vp]),
     ("rl_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _vp, _sz, _vp]),
+    ("rl_selftest_wait_timeout", _i, [_vp, _sz, ctypes.c_ulonglong, _vp]),
     ("rl_read_status", _i, [_vp, ctypes.POINTER(ctypes.c_int)]),
 ]
 

@@ -356,6 +356,25 @@ int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, cons
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+// ---- self-test of the bounded waits: one CTA waits on an mbarrier that nothing ever arrives on, with a
+// short limit, and must come back with an error record instead of hanging.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ CtaCtl ctl;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    ctl.abort = 0;
+    ctl.status = status;
+    ctl.limit_ns = limit_ns;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  // every thread waits for phase 0, which never completes; the first to run out of time aborts the CTA
+  const bool ok = mbar_wait(smem_u32(&bar), 0, &ctl, /*role=*/9, /*bar_id=*/0, /*idx=*/(int)threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x == 0 && status != nullptr) status[6] = ok ? 1 : 2;  // 2: the wait gave up, as it should
+}
+
 // ---- scratch for the allocation-free entry point: lives in the library's device image, one copy per
 // GPU that loads the library, held until the process exits.  In host code this name is only a handle
 // for cudaGetSymbolAddress, never a device address to pass to a kernel.
@@ -472,13 +491,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
     case RL_VARIANT_PREFILL_PAIR_PRESTATS: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
-    case 12: return RL_PAIR(192, 2, 6, 3, 3, A_TS_FOLD);
-    case 13: return RL_PAIR(256, 1, 6, 6, 3, A_TS_FOLD);
-    case 15: return RL_PAIR(256, 1, 6, 6, 1, A_TS_FOLD, true);
 #undef RL_PAIR
-    case 6: return RL_PREFILL(192, 3, A_TS_FOLD, 1);
-    case 7: return RL_PREFILL(192, 2, A_TS_FOLD, 1);
-    case 8: return RL_PREFILL(192, 4, A_TS_FOLD, 1);
     default: return RL_ERR_BAD_VARIANT;
   }
 #undef RL_PREFILL
@@ -576,6 +589,15 @@ int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
       A, nullptr, B, C, M, N, K, lda, ldb, ldc, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
       /*no_norm=*/true);
+}
+
+int rl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream) {
+  if (!workspace) return RL_ERR_NULL_POINTER;
+  if (workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return RL_ERR_BAD_SHAPE;  // keep the self-test short
+  wait_timeout_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(reinterpret_cast<int*>(workspace), limit_ns);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
 int rl_read_status(const void* workspace, int* detail) {

@@ -160,6 +160,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     }
     ctl->abort = 0;
     ctl->status = p.status;
+    ctl->limit_ns = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_w);

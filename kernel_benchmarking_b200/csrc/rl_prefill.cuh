@@ -150,6 +150,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     }
     ctl->abort = 0;
     ctl->status = p.status;
+    ctl->limit_ns = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
     prefetch_tmap(&tm_w);

@@ -135,6 +135,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
     ctl->abort = 0;
     ctl->status = p.status;
+    ctl->limit_ns = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_x);
     prefetch_tmap(&tm_w);

@@ -16,9 +16,10 @@ namespace rl {
 enum : int { RL_STATUS_INTS = 64 };
 enum DeviceError : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1, DEV_BAD_SMEM_ALIGNMENT = 2 };
 
-struct CtaCtl {            // lives in shared memory
-  volatile int abort;      // set by the first waiter that times out
-  int* status;             // global status block or nullptr
+struct CtaCtl {                 // lives in shared memory
+  volatile int abort;           // set by the first waiter that times out
+  int* status;                  // global status block or nullptr
+  unsigned long long limit_ns;  // how long a wait may last (0 = RL_WAIT_LIMIT_NS)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -72,7 +73,8 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, CtaCt
     if (mbar_try_wait(bar, parity)) return true;
     if (ctl->abort) return false;
     if ((++spins & 0xff) == 0) {
-      if (global_timer_ns() - t0 > RL_WAIT_LIMIT_NS) {
+      const unsigned long long limit = ctl->limit_ns ? ctl->limit_ns : RL_WAIT_LIMIT_NS;
+      if (global_timer_ns() - t0 > limit) {
         ctl->abort = 1;
         if (ctl->status != nullptr && atomicCAS(ctl->status, 0, (int)DEV_WAIT_TIMEOUT) == 0) {
           ctl->status[1] = role;

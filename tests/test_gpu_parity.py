@@ -358,3 +358,35 @@ def test_swiglu_golden_and_shapes(golden_dir):
         assert orc.rel_max_err(y.cpu(), ref) <= BF16_TOL
     with pytest.raises(ValueError):
         kb.rmsnorm_swiglu(x.to(DEV), gm.to(DEV), W[:200].contiguous().to(DEV), 1e-6)   # n not a multiple of 128
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """Failure detection: a wait that can never be satisfied runs out after its limit, leaves an error record
+    in the status block and the context stays usable (no trap, no hang)."""
+    import ctypes
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = torch.empty(4096, dtype=torch.uint8, device=DEV)
+    assert lib.rl_workspace_init(ws.data_ptr(), ws.numel(), stream) == _lib.RL_OK
+    assert lib.rl_selftest_wait_timeout(ws.data_ptr(), ws.numel(), 2_000_000, stream) == _lib.RL_OK   # 2 ms
+    detail = (ctypes.c_int * 8)()
+    assert lib.rl_read_status(ws.data_ptr(), detail) == _lib.RL_ERR_DEVICE_TIMEOUT
+    assert detail[0] == 1 and detail[1] == 9 and detail[6] == 2      # timeout, role 9, the waiters gave up
+    # the context is alive: clear the record and run the operator
+    assert lib.rl_workspace_init(ws.data_ptr(), ws.numel(), stream) == _lib.RL_OK
+    assert lib.rl_read_status(ws.data_ptr(), detail) == _lib.RL_OK
+    x, gm, W = orc.make_inputs(16, 256, 128, seed=3)
+    assert orc.rel_max_err(run(x, gm, W, 1e-6), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+
+
+@pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_column_parallel_two_gpus_nccl():
+    """W split over two GPUs, x replicated, y assembled with one NCCL all-gather: equals the oracle."""
+    import subprocess
+    import sys as _sys
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_column_parallel_worker.py")
+    r = subprocess.run([_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", worker],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
