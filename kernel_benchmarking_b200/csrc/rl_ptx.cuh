@@ -66,12 +66,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Returns true when the phase completed; false when the CTA is aborting (this
 // waiter timed out, or another one did).  role/bar_id/idx go to the status block.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, CtaCtl* ctl, int role, int bar_id,
-                                            int idx) {
+                                            int idx, uint32_t sleep_ns) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (ctl->abort) return false;
+    // waits that are long by design (an epilogue waiting out a whole main loop, a producer ahead of the MMA)
+    // back off so they do not take issue slots - and power - from the warps on the critical path
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((++spins & 0xff) == 0) {
       const unsigned long long limit = ctl->limit_ns ? ctl->limit_ns : RL_WAIT_LIMIT_NS;
       if (global_timer_ns() - t0 > limit) {
@@ -92,7 +95,8 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, CtaCt
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, CtaCtl* ctl, int role, int bar_id,
                                           int idx) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx);
+  // no back-off: measured, sleeping pollers (producer, epilogue) gained nothing and cost the decode kernel 3 %
+  return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx, 0u);
 }
 
 // One lane of a fully converged warp.  The TMA and MMA issue loops run with the whole warp
