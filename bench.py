@@ -215,6 +215,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--variant", default="auto", help="kernel variant name (see kernel_benchmarking_b200._lib.VARIANTS)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="M <= 64 workloads: time CUDA-graph replay instead of eager launches (measured: no faster, "
+                         "the call costs 11 us of host time against a 43 us kernel)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + timed steps (no clock-sampling spin, no e2e, no CPU baseline): for ncu")
     args = ap.parse_args()
@@ -276,11 +279,44 @@ def main():
             torch.cuda.synchronize()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    barrier()
+    # optional: replay a CUDA graph that holds one step per buffer set, as a serving loop would
+    use_graph = (bound == "hbm") and args.graph and not args.profile
+    eager_ms = None
+    if use_graph:
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        barrier()
+        eager_ms = e0.elapsed_time(e1) / args.steps
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(sets):
+                step(i)                      # workspace for this stream exists before capture starts
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(sets):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        replays = max(1, args.steps // sets)
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        e0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        timed_steps = replays * sets
+    else:
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        barrier()
+        timed_steps = args.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     kb.check_status()
@@ -288,7 +324,7 @@ def main():
         t = torch.tensor([ms_total], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    ms_step = ms_total / timed_steps
     flops = 2.0 * M * N * K
     if bound == "tensor":
         value, unit = world * flops / (ms_step * 1e-3) / 1e12, "TFLOP/s"
@@ -361,20 +397,24 @@ def main():
             "config": {"workload": args.workload, "M": M, "N_per_gpu": N, "K": K, "eps": 1e-6, "gamma": True,
                        "sharding": f"column-parallel x{world}, x replicated, no collective",
                        "l2": f"inputs larger than L2: {sets} rotating buffer sets of {step_bytes / 1e6:.0f} MB",
-                       "variant": args.variant},
+                       "variant": args.variant,
+                       "launch": "CUDA graph replay" if use_graph else "eager"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N,
                     "ms_per_step": e2e_ms, "note": "HostRMSNormLinear: x from pinned host memory and y back to pinned host "
                     "memory every step, copy-in / kernel / copy-out of consecutive steps overlapped on three streams; "
                     "W and gamma are weights, resident on the device"},
             # M > 128 and the FP8 path launch two kernels per step (row statistics / quantisation, then the GEMM)
-            "gpu_launches": args.steps * world * (2 if (fp8 or M > 128) else 1),
+            "gpu_launches": timed_steps * world * (2 if (fp8 or M > 128) else 1),
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peaks['source']}" + (" bf16 x 2 (no FP8 peak was measured)" if fp8 else ""),
                          "algorithmic_bytes": step_bytes, "algorithmic_flops": flops},
         }
         if gather_ms is not None:
             line["gather_ms"] = gather_ms
+        if eager_ms is not None:
+            line["eager_ms_per_step"] = eager_ms
+            line["steps"] = timed_steps
         if world == 1 and not args.no_cpu_baseline:
             rows, med, reps = cpu_reference_time(M, N, K)
             cores = torch.get_num_threads()

@@ -390,3 +390,28 @@ def test_column_parallel_two_gpus_nccl():
                         "--master-addr", "127.0.0.1", "--master-port", "29533", worker],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_decode_call_in_a_cuda_graph():
+    """The small-M call captured in a CUDA graph and replayed: same bits as the eager call."""
+    M, N, K = 8, 2048, 1024
+    x, gm, W = orc.make_inputs(M, N, K, seed=31)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y_eager = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    y_graph = torch.zeros_like(y_eager)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        kb.rmsnorm_linear(xd, gd, Wd, 1e-6, out=y_graph)      # creates this stream's workspace before capture
+        side.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            kb.rmsnorm_linear(xd, gd, Wd, 1e-6, out=y_graph)
+    torch.cuda.current_stream().wait_stream(side)
+    y_graph.zero_()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert torch.equal(y_graph, y_eager)
+    assert orc.rel_max_err(y_graph.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
