@@ -138,7 +138,7 @@ class ProfilingJob:
         ra = ref_args if ref_args is not None else [a.double() if isinstance(a, torch.Tensor) and a.is_floating_point()
                                                     else a for a in args]
         self.ref_out = kernels[ref](*[ra[i] for i in arg_mask[ref]])
-        self.ref_by_kernel = ref_by_kernel or {}   # e.g. the plain-GEMM lines are judged against a plain fp64 GEMM
+        self.ref_by_kernel = ref_by_kernel or {}   # e.g. the plain-GEMM lines are compared with a plain fp64 GEMM
 
     def run(self, ncu: bool = False, pause_s: float = 2.0) -> list:
         m, n, k = self.shape

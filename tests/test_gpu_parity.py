@@ -415,3 +415,41 @@ def test_decode_call_in_a_cuda_graph():
     kb.check_status()
     assert torch.equal(y_graph, y_eager)
     assert orc.rel_max_err(y_graph.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+
+
+def test_strided_operands():
+    """x, W and y as column slices of wider buffers (leading dimensions larger than the rows)."""
+    for (M, N, K) in [(200, 264, 192), (9, 264, 192)]:
+        x, gm, W = orc.make_inputs(M, N, K, seed=12)
+        xb = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+        Wb = torch.zeros(N, K + 128, dtype=torch.bfloat16, device=DEV)
+        xb[:, :K] = x.to(DEV)
+        Wb[:, :K] = W.to(DEV)
+        y = kb.rmsnorm_linear(xb[:, :K], gm.to(DEV), Wb[:, :K], 1e-6)
+        torch.cuda.synchronize()
+        kb.check_status()
+        assert orc.rel_max_err(y.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+
+
+def test_config4_whole_layer_on_one_gpu():
+    """16384 x 57344 x 8192 unsharded (x 268 MB, W 940 MB, y 1.88 GB): row sample against the CPU oracle,
+    column blocks against torch fp32 on the GPU."""
+    M, N, K = 16384, 57344, 8192
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    gm = (1 + 0.1 * torch.randn(K, generator=g)).bfloat16()
+    W = torch.empty(N, K, dtype=torch.bfloat16)
+    for n0 in range(0, N, 8192):
+        W[n0:n0 + 8192] = (torch.randn(8192, K, generator=g) * K ** -0.5).bfloat16()
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    torch.cuda.synchronize()
+    kb.check_status()
+    rows = torch.tensor([0, 1, 255, 256, 4097, 9999, 16000, 16383])
+    assert orc.rel_max_err(y[rows.to(DEV)].cpu(), orc.reference_fp32(x[rows], gm, W, 1e-6)) <= BF16_TOL
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for n0 in (0, 28672 - 128, 57344 - 256):
+        ref = orc.torch_rmsnorm_linear(xd.float(), gd.float(), Wd[n0:n0 + 256].float(), 1e-6)
+        assert orc.rel_max_err(y[:, n0:n0 + 256], ref) <= BF16_TOL
+    del y, xd, Wd
+    torch.cuda.empty_cache()
