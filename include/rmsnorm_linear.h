@@ -49,6 +49,7 @@ enum {
   RL_VARIANT_PREFILL_PAIR_N256 = 9,   /* CTA pairs (cta_group::2): 256 x 256 tiles, A operand through tensor memory */
   RL_VARIANT_PREFILL_PAIR_N192 = 10,  /* CTA pairs: 256 x 192 tiles, two accumulators (epilogue overlaps the next tile) */
   RL_VARIANT_PREFILL_PAIR_PRESTATS = 14, /* CTA pairs, 256 x 256: 1/rms per token from a row-statistics pre-pass (needs a workspace) */
+  RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS = 16, /* gamma == NULL only: 1/rms from the pre-pass, x straight from shared memory, two accumulators */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
   RL_VARIANT_DECODE = 20           /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
 };

@@ -37,6 +37,7 @@ VARIANTS = {
     "prefill_pair_n192": 10,
     "prefill_pair_direct": 11,
     "prefill_pair_prestats": 14,
+    "prefill_pair_direct_prestats": 16,
     "decode": 20,
 }
 

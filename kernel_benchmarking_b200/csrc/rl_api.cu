@@ -451,7 +451,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   const bool decode = (variant == RL_VARIANT_DECODE) || (variant == RL_VARIANT_AUTO && M <= 64);
   if (decode && M > 64) return RL_ERR_BAD_VARIANT;
   if (!decode && ((ldy & 7) || !aligned16(y))) return RL_ERR_ALIGNMENT;
-  const WsLayout wl = ws_layout(decode ? M : 65, N);
+  const WsLayout wl = ws_layout(decode || M > 65 ? M : 65, N);
   if (decode && !workspace) return RL_ERR_WORKSPACE;
   if (workspace && workspace_bytes < wl.total) return RL_ERR_WORKSPACE;
   DeviceInfo di;
@@ -473,7 +473,10 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   if (variant == RL_VARIANT_AUTO) {
     // with a workspace the pair kernel takes 1/rms from the (overlapped) row-statistics pass; without one it
     // accumulates the sums of squares itself
-    variant = (M > 128) ? (workspace ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_N256)
+    // and without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
+    // which frees tensor memory for a second accumulator
+    variant = (M > 128) ? (workspace ? (g ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS)
+                                     : RL_VARIANT_PREFILL_PAIR_N256)
                         : RL_VARIANT_PREFILL_TS_N192;
   }
 #define RL_PREFILL(BN, ST, AM, TG) \
@@ -491,6 +494,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
     case RL_VARIANT_PREFILL_PAIR_PRESTATS: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
+    case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT, true);
 #undef RL_PAIR
     default: return RL_ERR_BAD_VARIANT;
   }

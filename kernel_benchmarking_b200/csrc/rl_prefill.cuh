@@ -278,16 +278,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           if (has_gamma) {
             const uint4* g = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES);
             const int kvalid = p.K - kb * 64;  // >= 64 except in a ragged last block
+            if (kvalid >= 64) {
+              // the eight gamma loads back to back, no branch between them (a branch per load exposes each latency)
+              uint4 gv[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              if (c * 8 < kvalid) {
-                const uint4 gv = g[c];
-                v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv.x);
-                v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv.y);
-                v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv.z);
-                v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv.w);
-              } else {
-                v[4 * c + 0] = v[4 * c + 1] = v[4 * c + 2] = v[4 * c + 3] = 0u;
+              for (int c = 0; c < 8; ++c) gv[c] = g[c];
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv[c].x);
+                v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv[c].y);
+                v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv[c].z);
+                v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv[c].w);
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                if (c * 8 < kvalid) {
+                  const uint4 gv = g[c];
+                  v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv.x);
+                  v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv.y);
+                  v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv.z);
+                  v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv.w);
+                } else {
+                  v[4 * c + 0] = v[4 * c + 1] = v[4 * c + 2] = v[4 * c + 3] = 0u;
+                }
               }
             }
           }

@@ -31,12 +31,14 @@ namespace rl {
 
 // Optional timeline instrumentation (compile with -DRL_TRACE): clock64 stamps of the first
 // RL_TRACE_N k-blocks of CTA pair 0, laid out [rank][event][index]; RL_DEBUG switches turn
-// parts of the kernel off for experiments (results become wrong).
+// parts of the kernel off for experiments (results become wrong): 1 = no transform work; 64 = only the MMA
+// issue stamps and one stamp per tile, 64 + 16 = only the one per tile.  Keep switches out of inner loops: a
+// branch around each load of the transform alone slowed the whole kernel by a fifth.
 #ifdef RL_TRACE
 #define RL_TRACE_N 256
 #define RL_STAMP(ev, idx)                                                               \
   do {                                                                                  \
-    if (p.trace != nullptr && pair == 0 && (idx) < RL_TRACE_N)                          \
+    if (p.trace != nullptr && pair == 0 && (idx) < RL_TRACE_N && (!(p.debug & 64) || ((ev) == 2 && !(p.debug & 16)) || (ev) == 5)) \
       p.trace[((int)rank * 8 + (ev)) * RL_TRACE_N + (idx)] = clock64();                 \
   } while (0)
 #define RL_DEBUG(bit) ((p.debug & (bit)) != 0)
@@ -273,19 +275,45 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           if (has_gamma) {
             const uint4* g = reinterpret_cast<const uint4*>(smem + Cfg::OFF_G + s * Cfg::G_BYTES);
             const int kvalid = p.K - kb * 64;
+            if (kvalid >= 64) {
+              // whole k-block: the eight gamma loads issued back to back with no branch between them (a branch
+              // per load left each load's latency exposed: 640 cycles per k-block instead of about 100)
+              uint4 gv[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              if (c * 8 < kvalid) {
-                const uint4 gv = g[c];
-                v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv.x);
-                v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv.y);
-                v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv.z);
-                v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv.w);
-              } else {
-                v[4 * c + 0] = v[4 * c + 1] = v[4 * c + 2] = v[4 * c + 3] = 0u;
+              for (int c = 0; c < 8; ++c) gv[c] = g[c];
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv[c].x);
+                v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv[c].y);
+                v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv[c].z);
+                v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv[c].w);
+              }
+            } else {
+              // last, partial k-block (K not a multiple of 64): the gamma slice ends at K; x beyond K is zero-filled
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                if (c * 8 < kvalid) {
+                  const uint4 gv = g[c];
+                  v[4 * c + 0] = mul_bf16x2(v[4 * c + 0], gv.x);
+                  v[4 * c + 1] = mul_bf16x2(v[4 * c + 1], gv.y);
+                  v[4 * c + 2] = mul_bf16x2(v[4 * c + 2], gv.z);
+                  v[4 * c + 3] = mul_bf16x2(v[4 * c + 3], gv.w);
+                } else {
+                  v[4 * c + 0] = v[4 * c + 1] = v[4 * c + 2] = v[4 * c + 3] = 0u;
+                }
               }
             }
           }
+#ifdef RL_TRACE
+          if (q == 0 && lane == 0 && p.trace != nullptr && pair == 0 && j < RL_TRACE_N && !(p.debug & 64)) {
+            long long tck;  // ordered behind the multiplies (so behind the shared-memory loads) by a fake operand
+            uint32_t fold = 0;
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) fold ^= v[jj];
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(fold));
+            p.trace[((int)rank * 8 + 1) * RL_TRACE_N + j] = tck;
+          }
+#endif
           __syncwarp();
           tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::A_COL0 + (j % ASLOTS) * 32, v);
           tmem_wait_st();

@@ -64,12 +64,12 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
                                      "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
-                                     "prefill_pair_direct", "prefill_pair_prestats"])
+                                     "prefill_pair_direct", "prefill_pair_prestats", "prefill_pair_direct_prestats"])
 @pytest.mark.parametrize("has_gamma", [False, True])
 @pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
 def test_every_prefill_variant(variant, has_gamma, M, N, K):
-    if variant == "prefill_pair_direct" and has_gamma:
-        with pytest.raises(ValueError):   # that variant reads x straight from shared memory: no gamma fold
+    if variant in ("prefill_pair_direct", "prefill_pair_direct_prestats") and has_gamma:
+        with pytest.raises(ValueError):   # those variants read x straight from shared memory: no gamma fold
             x, gm, W = orc.make_inputs(256, 256, 64, gamma=True)
             kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, variant=variant)
         return
