@@ -48,7 +48,9 @@ enum {
   RL_VARIANT_PREFILL_SS_N128 = 5,
   RL_VARIANT_PREFILL_PAIR_N256 = 9,   /* CTA pairs (cta_group::2): 256 x 256 tiles, A operand through tensor memory */
   RL_VARIANT_PREFILL_PAIR_N192 = 10,  /* CTA pairs: 256 x 192 tiles, two accumulators (epilogue overlaps the next tile) */
-  RL_VARIANT_PREFILL_PAIR_PRESTATS = 14, /* CTA pairs, 256 x 256: 1/rms per token from a row-statistics pre-pass (needs a workspace) */
+  RL_VARIANT_PREFILL_PAIR_PRESTATS = 14, /* CTA pairs, 256 x 256: 1/rms per token from a row-statistics pre-pass (needs a workspace);
+                                            the tiles of a partly filled last round are split along K across the idle pairs */
+  RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE = 15, /* as 14, every tile computed whole by one pair */
   RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS = 16, /* gamma == NULL only: 1/rms from the pre-pass, x straight from shared memory, two accumulators */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
   RL_VARIANT_DECODE = 20           /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
@@ -66,6 +68,12 @@ const char* rl_error_string(int code);
  * arithmetic, needs no GPU.  No reference counterpart (the reference's kernels
  * allocate through their DSL runtimes). */
 size_t rl_workspace_bytes(int M, int N, int K, int w_dtype);
+
+/* How the M > 128 pre-pass kernels treat the last, partly filled round of 256 x 256 tiles on `pairs` CTA pairs
+ * (74 on a B200): *tail_tiles tiles are each cut along K into *split (2 or 4) slices computed by different pairs
+ * and summed in slice order; 0 / 0 = every tile computed whole.  Pure arithmetic, needs no GPU.  No reference
+ * counterpart (its kernels leave scheduling to their DSL compilers). */
+int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* split);
 
 /* Zero the workspace (status block and tile counters) on `stream`.  Must run
  * once before the first use of a workspace; kernels leave it clean afterwards. */

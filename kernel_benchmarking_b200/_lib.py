@@ -37,6 +37,7 @@ VARIANTS = {
     "prefill_pair_n192": 10,
     "prefill_pair_direct": 11,
     "prefill_pair_prestats": 14,
+    "prefill_pair_prestats_whole": 15,
     "prefill_pair_direct_prestats": 16,
     "decode": 20,
 }
@@ -47,6 +48,7 @@ SYMBOLS = [
     ("rl_version", _i, []),
     ("rl_error_string", ctypes.c_char_p, [_i]),
     ("rl_workspace_bytes", _sz, [_i, _i, _i, _i]),
+    ("rl_plan_tail_split", _i, [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     ("rl_workspace_init", _i, [_vp, _sz, _vp]),
     ("rl_rmsnorm_linear_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
     ("rl_rmsnorm_linear_fp8w", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),

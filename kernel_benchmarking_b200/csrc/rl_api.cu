@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces they replace: include/rmsnorm_linear.h
 #include "../../include/rmsnorm_linear.h"
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -131,15 +132,25 @@ int device_info(DeviceInfo* out) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// fp32 partial blocks of k-split tail tiles: one 128 x 256 block per CTA of the persistent grid
+constexpr size_t TAIL_SLOT_BYTES = (size_t)128 * 256 * 4;
+constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
+
 struct WsLayout {
   size_t counters_off, ssq_off, partials_off, total;
+  size_t rstd_off, tail_off, min_total;  // M > 64 only
 };
 WsLayout ws_layout(int M, int N) {
   WsLayout w{};
   if (M > 64) {
-    // status block, the (untouched) tile-counter region every shape keeps at the same place, then 1/rms per
-    // token for the PRESTATS kernels
-    w.total = STATUS_BYTES + COUNTER_BYTES + align_up((size_t)M * 4, 256);
+    // status block, the counter region every shape keeps at the same place (zero between launches), 1/rms per
+    // token for the PRESTATS kernels, then the partial blocks of k-split tail tiles.  A workspace that ends
+    // before the partial blocks (min_total) still works: the tail tiles are then computed whole.
+    w.counters_off = STATUS_BYTES;
+    w.rstd_off = STATUS_BYTES + COUNTER_BYTES;
+    w.tail_off = w.rstd_off + align_up((size_t)M * 4, 256);
+    w.min_total = w.tail_off;
+    w.total = w.tail_off + TAIL_BYTES;
     return w;
   }
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -175,10 +186,25 @@ int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, voi
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+// What to do with the last, partly filled round of tiles.  `tiles` tiles are dealt to `max_pairs` CTA pairs; r =
+// tiles % max_pairs of them form the last round, which costs a whole tile's time however few they are.  Cut
+// along K into S slices, r * S pairs share that work and then spend a few microseconds exchanging partial
+// sums; worth it when the slices are long enough (KB k-blocks of 64 in the whole K).
+struct TailPlan {
+  int tiles, split;
+};
+TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
+  const int r = (int)(tiles % max_pairs);
+  if (r == 0 || KB < 32) return TailPlan{0, 0};
+  if ((long long)r * 4 <= max_pairs && r * 4 * 2 <= RL_MAX_CTAS) return TailPlan{r, 4};
+  if ((long long)r * 2 <= max_pairs && r * 2 * 2 <= RL_MAX_CTAS) return TailPlan{r, 2};
+  return TailPlan{0, 0};
+}
+
 template <class Cfg>
 int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                         int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st,
-                        bool no_norm = false) {
+                        bool no_norm = false, size_t ws_bytes = 0, bool split_tail = true) {
   CUtensorMap tx, tw, ty;
   int rc;
   if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
@@ -196,7 +222,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.status = status;
   if (Cfg::PRESTATS && !no_norm) {
     if (status == nullptr) return RL_ERR_WORKSPACE;
-    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + STATUS_BYTES + COUNTER_BYTES);
+    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + ws_layout(M > 65 ? M : 65, N).rstd_off);
     rowstats_kernel<<<(M + 3) / 4, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), rstd, M, K, ldx, eps);
     p.row_rstd = rstd;
   }
@@ -228,7 +254,18 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
     max_pairs_cache[dev & 63] = n;
   }
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
-  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && split_tail && status != nullptr) {
+    const WsLayout wl = ws_layout(M > 65 ? M : 65, N);
+    const TailPlan tp = plan_tail(tiles, max_pairs, (K + 63) / 64);
+    if (tp.split > 1 && ws_bytes >= wl.total) {
+      p.tail_tiles = tp.tiles;
+      p.tail_split = tp.split;
+      p.tail_counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(status) + wl.counters_off);
+      p.tail_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + wl.tail_off);
+      if (tiles < max_pairs) pairs = tp.tiles * tp.split;  // fewer tiles than pairs: every tile is cut
+    }
+  }
   if (Cfg::PRESTATS) {
     // behind rowstats_kernel with programmatic stream serialisation: the GEMM streams its tiles while the
     // row statistics are still being computed and waits only where it first reads them
@@ -434,6 +471,15 @@ size_t rl_workspace_bytes(int M, int N, int K, int w_dtype) {
   return ws_layout(M, N).total;
 }
 
+int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* split) {
+  if (M <= 0 || N <= 0 || K <= 0 || pairs <= 0) return RL_ERR_BAD_SHAPE;
+  const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  const TailPlan tp = plan_tail(tiles, pairs, (K + 63) / 64);
+  if (tail_tiles) *tail_tiles = tp.tiles;
+  if (split) *split = tp.split;
+  return RL_OK;
+}
+
 int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace) return RL_ERR_NULL_POINTER;
   if (workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
@@ -453,7 +499,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   if (!decode && ((ldy & 7) || !aligned16(y))) return RL_ERR_ALIGNMENT;
   const WsLayout wl = ws_layout(decode || M > 65 ? M : 65, N);
   if (decode && !workspace) return RL_ERR_WORKSPACE;
-  if (workspace && workspace_bytes < wl.total) return RL_ERR_WORKSPACE;
+  if (workspace && workspace_bytes < (decode ? wl.total : wl.min_total)) return RL_ERR_WORKSPACE;
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
@@ -479,6 +525,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
                                      : RL_VARIANT_PREFILL_PAIR_N256)
                         : RL_VARIANT_PREFILL_TS_N192;
   }
+  const bool split_tail = (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
 #define RL_PREFILL(BN, ST, AM, TG) \
   launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
   switch (variant) {
@@ -489,11 +536,12 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 4, A_SS_FOLD, 2) : RL_PREFILL(128, 4, A_SS_DIRECT, 2);
 #define RL_PAIR(BN, NACC, ST, AS, TG, AM, ...) \
   launch_prefill_pair<PairCfg<BN, NACC, ST, AS, TG, AM, ##__VA_ARGS__>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, \
-                                                                       di.sms, st)
+                                                                       di.sms, st, false, workspace_bytes, split_tail)
     case RL_VARIANT_PREFILL_PAIR_N256: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
     case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
-    case RL_VARIANT_PREFILL_PAIR_PRESTATS: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
+    case RL_VARIANT_PREFILL_PAIR_PRESTATS:
+    case RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
     case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT, true);
 #undef RL_PAIR
     default: return RL_ERR_BAD_VARIANT;
@@ -568,7 +616,7 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7) || (N & 127) || !aligned16(x) || !aligned16(W) || !aligned16(y) ||
       (gamma && !aligned16(gamma)))
     return RL_ERR_ALIGNMENT;
-  const size_t need = ws_layout(65 > M ? 65 : M, N).total;
+  const size_t need = ws_layout(65 > M ? 65 : M, N).min_total;
   if (!workspace || workspace_bytes < need) return RL_ERR_WORKSPACE;
   DeviceInfo di;
   int rc = device_info(&di);
@@ -592,7 +640,7 @@ int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
   return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
       A, nullptr, B, C, M, N, K, lda, ldb, ldc, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
-      /*no_norm=*/true);
+      /*no_norm=*/true, workspace_bytes);
 }
 
 int rl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream) {

@@ -69,7 +69,7 @@ struct PairCfg {
   static constexpr int OFF_EPI = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_G = OFF_EPI + 2 * EPI_BYTES;
   static constexpr int OFF_RS = OFF_G + (AMODE_ == A_TS_FOLD ? STAGES * G_BYTES : 0);
-  static constexpr int OFF_BAR = OFF_RS + TG * NACC * 128 * 4;
+  static constexpr int OFF_BAR = OFF_RS + (PRESTATS_ ? 0 : TG * NACC * 128 * 4);
   static constexpr int NUM_BARS = 3 * STAGES + 4 * NACC;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64;  // no alignment slack: the kernel checks the base instead
@@ -87,6 +87,36 @@ struct PairCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
+// One work item of a CTA pair: a whole tile (slice < 0, k-blocks [0, KB)), or one k-slice of a tail tile.
+//
+// Tiles are dealt round-robin, tile t to pair t % n_pairs.  A k-block of a 256 x 256 tile costs the tensor
+// pipe the same ~650 cycles whatever the tile's width (the MMA instruction has a fixed cost), so the only way
+// to spread the tiles of a partly filled last round over the idle pairs is along K: with tail_split = S each
+// of the last `tail_tiles` tiles is cut into S k-slices that S different pairs compute at the same time (pair
+// u takes slice u % S of tail tile u / S); the S partial accumulators meet in the epilogue.
+struct PairItem {
+  int t, kb0, kb1, slice;
+};
+template <bool TAIL>
+__device__ __forceinline__ bool pair_item(const PrefillParams& p, int pair, int n_pairs, int total_tiles, int KB, int i,
+                                          PairItem& w) {
+  w.t = pair + i * n_pairs;
+  w.kb0 = 0;
+  w.kb1 = KB;
+  w.slice = -1;
+  if (!TAIL || p.tail_split <= 1) return w.t < total_tiles;
+  const int t_main = total_tiles - p.tail_tiles;  // a multiple of n_pairs (or 0)
+  if (w.t < t_main) return true;
+  const int u = w.t - t_main;
+  if (u >= p.tail_tiles * p.tail_split) return false;
+  const int S = p.tail_split;
+  w.t = t_main + u / S;
+  w.slice = u % S;
+  w.kb0 = (int)(((long long)w.slice * KB) / S);
+  w.kb1 = (int)(((long long)(w.slice + 1) * KB) / S);
+  return true;
+}
+
 template <class Cfg>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::THREADS, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
@@ -95,6 +125,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
   constexpr bool PRESTATS = Cfg::PRESTATS;
   constexpr bool SWIGLU = Cfg::SWIGLU;
+  // k-split tail tiles: 1/rms must come from outside (a slice sees only part of a row) and the epilogue is plain
+  constexpr bool TAIL = PRESTATS && !SWIGLU && BN == 256;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
@@ -111,6 +143,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * STAGES + NACC + a); };
   auto bar_rsfull = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 * NACC + a); };
   auto bar_rsfree = [&](int a) { return bar0 + 8u * (3 * STAGES + 3 * NACC + a); };
+  const uint32_t bar_tail = sbase + Cfg::OFF_MISC + 48u;  // partial blocks of a k-split tile landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_MISC);
   volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
@@ -135,6 +168,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       mbar_init(bar_rsfull(a), 4 * TG);
       mbar_init(bar_rsfree(a), 4);
     }
+    mbar_init(bar_tail, 1);
     ctl->abort = 0;
     ctl->status = p.status;
     ctl->limit_ns = 0;
@@ -160,10 +194,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     bool ok = true;
     [[maybe_unused]] int jp = 0;
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
-    for (int t = pair; ok && t < total_tiles; t += n_pairs) {
+    PairItem w;
+    for (int i = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i, w); ++i) {
       int mt, nt;
-      prefill_tile_coords(t, p, mt, nt);
-      for (int kb = 0; kb < KB; ++kb) {
+      prefill_tile_coords(w.t, p, mt, nt);
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
         if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
         if (elect_one()) {
           RL_STAMP(0, jp);
@@ -192,8 +227,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       int s = 0, aslot = 0;
       uint32_t ph = 0;
       bool ok = true;
-      int it = 0;
-      for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it) {
+      PairItem w;
+      for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
         const int acc = (NACC == 2) ? (it & 1) : 0;
         const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
         if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1u, ctl, 1, 3 * STAGES + NACC + acc, it)) break;
@@ -202,21 +237,21 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         // The issue loop sets the tensor cores' pace: one barrier wait per k-block, the poll for the
         // next slot started before this slot's MMAs are issued, and one predicated issue block.
         uint32_t ready_now = mbar_try_wait(bar_ready(s), ph);
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ready_now) {
             if (!mbar_wait(bar_ready(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
           }
-          if (lane == 0) RL_STAMP(2, it * KB + kb);
+          if (lane == 0) RL_STAMP(2, it * KB + kb - w.kb0);
           tc_fence_after();
           const int sn = (s + 1 == STAGES) ? 0 : s + 1;
           const uint32_t phn = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
           ready_now = mbar_try_wait(bar_ready(sn), phn);  // next k-block (or the next tile's first)
           if (TS) {
             umma_kblock_ts_pair(d, tmem_base + Cfg::A_COL0 + aslot * 32, bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)),
-                                idesc, (uint32_t)(kb != 0), bar_empty(s), leader);
+                                idesc, (uint32_t)(kb != w.kb0), bar_empty(s), leader);
           } else {
             umma_kblock_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
-                                bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != 0), bar_empty(s),
+                                bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != w.kb0), bar_empty(s),
                                 leader);
           }
           s = sn;
@@ -236,14 +271,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t swz = (uint32_t)(row & 7);
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
     bool ok = true;
-    int it = 0;
-    int j_base = 0;
-    for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it, j_base += KB) {
+    int j_base = 0;  // k-blocks this pair has been through: ring slot and phase follow from it
+    PairItem w;
+    for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it, j_base += w.kb1 - w.kb0) {
       const int acc = (NACC == 2) ? (it & 1) : 0;
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
       float2 ss2 = make_float2(0.f, 0.f);
-      for (int kb = (grp - j_base % TG + TG) % TG; kb < KB; kb += TG) {
-        const int j = j_base + kb;
+      for (int kb = w.kb0 + (grp - j_base % TG + TG) % TG; kb < w.kb1; kb += TG) {
+        const int j = j_base + kb - w.kb0;
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
         ok = mbar_wait(bar_fullA(s), ph, ctl, 2, s, kb);
@@ -342,11 +377,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t lead_tempty0 = mapa_shared(bar_tempty(0), 0);
     const uint64_t pol_y = l2_policy_evict_first();
     bool ok = true;
-    int it = 0;
     uint32_t chunk_no = 0;
-    for (int t = pair; ok && t < total_tiles; t += n_pairs, ++it) {
+    PairItem w;
+    for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
       int mt, nt;
-      prefill_tile_coords(t, p, mt, nt);
+      prefill_tile_coords(w.t, p, mt, nt);
       const int acc = (NACC == 2) ? (it & 1) : 0;
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
       float r_pre = 0.f;
@@ -393,7 +428,125 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
       };
       const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      if constexpr (SWIGLU) {
+      bool tail_done = false;
+      if constexpr (TAIL) {
+        if (w.slice >= 0) {
+          // ---- one k-slice of a tail tile (always this pair's last item).  The S contributors of a tile each
+          // finish 1/S of its columns: a CTA writes the fp32 partials of the other contributors' columns to the
+          // workspace, announces it, waits until all S have (they run at the same time: the grid is no larger
+          // than the device holds), pulls the S - 1 other partials of its own columns through the idle operand
+          // ring and adds them to its own in slice order, so the result does not depend on who came first.
+          tail_done = true;
+          const int S = p.tail_split;                     // 2 or 4
+          const int nch = (BN / 64) / S;                  // 64-column chunks this CTA finishes
+          const int c_lo = w.slice * nch;
+          const int tl = w.t - (total_tiles - p.tail_tiles);
+          unsigned* cnt = p.tail_counters + 2 * (tl * 2 + (int)rank);  // [0] partials written, [1] waits passed
+          constexpr int SLOT_F4 = 128 * BN / 4;                        // float4 per (tile, slice, rank) block
+          constexpr uint32_t PART_BYTES = 64 * 128 * 4;                // 64 columns of a block: contiguous
+          static_assert(3 * PART_BYTES <= (uint32_t)Cfg::OFF_EPI, "partial buffers fit in the operand ring");
+          // block layout [column / 4][row] float4: a warp's 32 rows of one column group are 512 contiguous bytes
+          float4* slot0 = reinterpret_cast<float4*>(p.tail_partials) + (size_t)(tl * S * 2 + (int)rank) * SLOT_F4;
+          float4* mine = slot0 + (size_t)w.slice * 2 * SLOT_F4;
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            if (c >= c_lo && c < c_lo + nch) continue;    // my own columns stay in tensor memory
+            uint32_t v0[32], v1[32];
+            tmem_ld32(trow + c * 64, v0);
+            tmem_ld32(trow + c * 64 + 32, v1);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              mine[(c * 16 + j) * 128 + row] =
+                  make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]), __uint_as_float(v0[4 * j + 2]),
+                              __uint_as_float(v0[4 * j + 3]));
+              mine[(c * 16 + 8 + j) * 128 + row] =
+                  make_float4(__uint_as_float(v1[4 * j]), __uint_as_float(v1[4 * j + 1]), __uint_as_float(v1[4 * j + 2]),
+                              __uint_as_float(v1[4 * j + 3]));
+            }
+          }
+          __threadfence();
+          named_bar_sync(1, 128);
+          if (epi_tid == 0) {
+            atomicAdd(cnt, 1u);
+            const bool good = global_count_wait(cnt, (unsigned)S, ctl, 3, 100 + tl, it);
+            if (good) {
+              __threadfence();
+              asm volatile("fence.proxy.async.global;" ::: "memory");  // the bulk copies below read what others wrote
+              // the other contributors' partials of my columns: one bulk copy of 32 KB per (slice, chunk)
+              mbar_expect_tx(bar_tail, (uint32_t)((S - 1) * nch) * PART_BYTES);
+              int b = 0;
+              for (int sl = 0; sl < S; ++sl) {
+                if (sl == w.slice) continue;
+                for (int c = 0; c < nch; ++c, ++b)
+                  bulk_load_1d(sbase + (uint32_t)b * PART_BYTES,
+                               slot0 + (size_t)sl * 2 * SLOT_F4 + (size_t)(c_lo + c) * 16 * 128, PART_BYTES, bar_tail);
+              }
+              // the last of the S to get here puts the pair of counters back to zero for the next launch
+              if (atomicAdd(cnt + 1, 1u) == (unsigned)(S - 1)) {
+                cnt[0] = 0u;
+                cnt[1] = 0u;
+              }
+            }
+            *epi_go = good ? 1 : 0;
+            tma_store_wait_read<0>();  // earlier tiles' stores are done with the staging tiles
+          }
+          named_bar_sync(2, 128);
+          ok = (*epi_go != 0);
+          if (!ok) break;
+          ok = mbar_wait(bar_tail, 0u, ctl, 3, 200 + tl, it);
+          named_bar_sync(3, 128);
+          if (epi_tid == 0) *epi_go = ctl->abort ? 0 : 1;
+          named_bar_sync(4, 128);
+          ok = (*epi_go != 0);
+          if (!ok) break;
+          const int m0 = mt * 256 + (int)rank * 128;
+#pragma unroll 1
+          for (int c = 0; c < nch; ++c) {
+            uint8_t* stage = smem + Cfg::OFF_EPI + (c & 1) * Cfg::EPI_BYTES;
+            uint32_t o[2][16];
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) {  // 16 columns at a time keeps the register count of the hot loops
+              uint32_t own[16];
+              tmem_ld16(trow + (c_lo + c) * 64 + qq * 16, own);
+              float a[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a[j] = 0.f;
+              tmem_wait_ld();
+              int b = 0;
+#pragma unroll 1
+              for (int sl = 0; sl < S; ++sl) {  // slice order, this CTA's own slice in its place
+                if (sl == w.slice) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) a[j] += __uint_as_float(own[j]);
+                } else {
+                  const float4* ps = reinterpret_cast<const float4*>(smem + (size_t)(b * nch + c) * PART_BYTES) +
+                                     (qq * 4) * 128 + row;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float4 d4 = ps[j * 128];
+                    a[4 * j] += d4.x; a[4 * j + 1] += d4.y; a[4 * j + 2] += d4.z; a[4 * j + 3] += d4.w;
+                  }
+                  ++b;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[qq >> 1][(qq & 1) * 8 + j] = pack_bf16x2(a[2 * j] * r, a[2 * j + 1] * r);
+            }
+            sts64(stage, o[0], o[1]);
+            fence_proxy_async_smem();
+            named_bar_sync(2, 128);
+            if (epi_tid == 0) {
+              const int n0 = nt * BN + (c_lo + c) * 64;
+              if (n0 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage), n0, m0, pol_y);
+              tma_store_commit();
+            }
+          }
+        }
+      }
+      if (tail_done) {
+        // the slice's columns were finished above
+      } else if constexpr (SWIGLU) {
         // p.N = n output channels; this tile covers channels nt*128 .. +127: gate in columns [0,128), up in [128,256)
         uint8_t* stage0 = smem + Cfg::OFF_EPI;
         uint8_t* stage1 = smem + Cfg::OFF_EPI + Cfg::EPI_BYTES;

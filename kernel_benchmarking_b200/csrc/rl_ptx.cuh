@@ -99,6 +99,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, CtaCtl*
   return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx, 0u);
 }
 
+// Bounded wait for a counter in global memory to reach `target`.  Only for counters bumped by CTAs of the
+// same launch (a persistent grid no larger than the device holds at once, so every CTA is running or about
+// to).  Same time limit and status record as the barrier waits.
+__device__ __noinline__ bool global_count_wait(const unsigned* cnt, unsigned target, CtaCtl* ctl, int role, int id,
+                                               int idx) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+    if (v >= target) return true;
+    if (ctl->abort) return false;
+    __nanosleep(32);
+    if ((++spins & 0xff) == 0) {
+      const unsigned long long limit = ctl->limit_ns ? ctl->limit_ns : RL_WAIT_LIMIT_NS;
+      if (global_timer_ns() - t0 > limit) {
+        ctl->abort = 1;
+        if (ctl->status != nullptr && atomicCAS(ctl->status, 0, (int)DEV_WAIT_TIMEOUT) == 0) {
+          ctl->status[1] = role;
+          ctl->status[2] = id;
+          ctl->status[3] = (int)blockIdx.x;
+          ctl->status[4] = idx;
+          ctl->status[5] = (int)v;
+          __threadfence();
+        }
+        return false;
+      }
+    }
+  }
+}
+
 // One lane of a fully converged warp.  The TMA and MMA issue loops run with the whole warp
 // converged and only the issuing instructions predicated on this: a loop run by a single
 // lane inside a divergent branch keeps descriptors out of the uniform datapath and issues

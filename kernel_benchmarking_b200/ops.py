@@ -181,7 +181,8 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = N
         return out
     stream = _stream_ptr(a.device)
     with _on_device(a.device):
-        ws = _workspace(a.device, 256, stream)
+        # sized like the fused operator's: with room for the partial blocks of a k-split last round of tiles
+        ws = _workspace(a.device, _lib.load().rl_workspace_bytes(max(M, 65), N, K, _lib.RL_W_BF16), stream)
         rc = _lib.load().rl_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                                       out.stride(0), ws.data_ptr(), ws.numel(), stream)
     _lib.check(rc, "rl_gemm_bf16")

@@ -29,10 +29,11 @@ def main():
         ref = orc.reference_fp32(x, gm, W, 1e-6)
         err = orc.rel_max_err(y.cpu(), ref)
         ok = ok and y.shape == (M, N) and err <= 1e-2
-        # the single-GPU kernel on the whole weight gives the same columns bit for bit (M > 64: same tile arithmetic)
+        # the single-GPU kernel on the whole weight gives the same columns: to one bf16 ulp (2^-7), since tiles of
+        # the last round may be summed in k-slices and which tiles those are depends on the shard's tile count
         if M > 64 and rank == 0:
             y_full = kb.rmsnorm_linear(x.to(dev), gm.to(dev), W.to(dev), 1e-6)
-            ok = ok and torch.equal(y_full[:, op.n0:op.n1], y_local)
+            ok = ok and orc.rel_max_err(y_full[:, op.n0:op.n1], y_local.float()) <= 2.0 ** -7
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

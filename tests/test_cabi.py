@@ -42,7 +42,9 @@ def test_version_and_error_strings(lib):
 
 def test_workspace_bytes_is_pure_arithmetic(lib):
     small = lib.rl_workspace_bytes(4096, 6144, 4096, 0)
-    assert small == 256 + 65536 + 4096 * 4  # status block + tile-counter region + one 1/rms per token
+    # status block + counter region + one 1/rms per token + one 128 x 256 fp32 partial block per CTA of the
+    # largest grid (160) for the k-split tiles of a partly filled last round
+    assert small == 256 + 65536 + 4096 * 4 + 160 * 128 * 256 * 4
     w16 = lib.rl_workspace_bytes(16, 28672, 4096, 0)
     w1 = lib.rl_workspace_bytes(1, 28672, 4096, 0)
     w64 = lib.rl_workspace_bytes(64, 28672, 4096, 0)
@@ -50,6 +52,33 @@ def test_workspace_bytes_is_pure_arithmetic(lib):
     # the counter region does not move with N: a workspace stays valid across shapes
     assert lib.rl_workspace_bytes(16, 128, 64, 0) == w16
     assert w64 < 64 << 20
+
+
+def _plan(lib, M, N, K, pairs=74):
+    a, b = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert lib.rl_plan_tail_split(M, N, K, pairs, ctypes.byref(a), ctypes.byref(b)) == 0
+    return a.value, b.value
+
+
+def test_tail_split_plan(lib):
+    """Which tiles of the M > 128 kernels are cut along K: those of a last round that fills at most half the CTA
+    pairs, in 4 when a quarter of the pairs is enough, else in 2, and only when K is long enough to pay for the
+    exchange of partial sums."""
+    assert _plan(lib, 16384, 28672, 8192) == (0, 0)        # 7168 tiles = 96.9 rounds: last round nearly full
+    assert _plan(lib, 256 * 74, 256, 4096) == (0, 0)       # exactly one round
+    assert _plan(lib, 512, 512, 1024) == (0, 0)            # K too short
+    assert _plan(lib, 4096, 6144, 4096) == (14, 4)         # the prefill benchmark shape: 384 tiles = 5 rounds + 14
+    assert _plan(lib, 4096, 4096, 4096) == (34, 2)         # 256 tiles = 3 rounds + 34
+    assert _plan(lib, 16384, 7168, 8192) == (16, 4)        # one of eight shards of the MLP layer: 1792 = 24 x 74 + 16
+    assert _plan(lib, 512, 1024, 4096) == (8, 4)           # fewer tiles than pairs
+    assert _plan(lib, 8192, 8192, 8192) == (0, 0)          # 1024 = 13 x 74 + 62: more than half a round
+    for pairs in (1, 7, 60, 64, 74, 80):
+        for (M, N) in [(4096, 6144), (300, 520), (8192, 14336), (1000, 1032)]:
+            tiles = ((M + 255) // 256) * ((N + 255) // 256)
+            tail, split = _plan(lib, M, N, 4096, pairs)
+            assert (tail, split) == (0, 0) or (tail == tiles % pairs and split in (2, 4) and tail * split <= pairs
+                                               and 2 * tail * split <= 160)
+    assert lib.rl_plan_tail_split(0, 1, 1, 74, None, None) != 0
 
 
 def test_argument_validation_needs_no_gpu(lib):

@@ -15,6 +15,7 @@ from oracle import rmsnorm_linear_oracle as orc
 
 pytestmark = pytest.mark.gpu
 BF16_TOL = 1e-2
+ONE_ULP = 2.0 ** -7   # largest step between neighbouring bf16 values, relative to the value
 DEV = "cuda:0"
 
 
@@ -64,7 +65,8 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
                                      "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
-                                     "prefill_pair_direct", "prefill_pair_prestats", "prefill_pair_direct_prestats"])
+                                     "prefill_pair_direct", "prefill_pair_prestats", "prefill_pair_direct_prestats",
+                                     "prefill_pair_prestats_whole"])
 @pytest.mark.parametrize("has_gamma", [False, True])
 @pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
 def test_every_prefill_variant(variant, has_gamma, M, N, K):
@@ -126,6 +128,56 @@ def test_bad_arguments_raise():
     assert kb.rmsnorm_linear(x[:0], gm, W).shape == (0, 64)
 
 
+def _tail_plan(M, N, K, pairs=74):
+    import ctypes
+    a, b = ctypes.c_int(), ctypes.c_int()
+    _lib.check(_lib.load().rl_plan_tail_split(M, N, K, pairs, ctypes.byref(a), ctypes.byref(b)), "rl_plan_tail_split")
+    return a.value, b.value
+
+
+@pytest.mark.parametrize("M,N,K,has_gamma", [
+    (512, 1024, 4096, True),     # fewer tiles than CTA pairs: every tile is split in 4
+    (300, 520, 2048, False),     # ragged rows and columns, no gamma (the shared-memory operand kernel)
+    (2560, 4096, 2056, True),    # two full rounds, then 12 tiles split in 4; the last k-block is partial
+    (4096, 4096, 4096, True),    # 3.46 rounds: 34 tail tiles split in 2
+    (1024, 2304, 8192, True),    # long K
+    (4096, 6144, 4096, False),   # the prefill benchmark shape without gamma
+])
+def test_tail_tiles_split_along_k(M, N, K, has_gamma):
+    """The last, partly filled round of tiles is cut along K across CTA pairs and the partial sums are exchanged
+    through the workspace.  Same results as whole tiles to one bf16 ulp, within tolerance of the reference, and
+    identical from run to run whichever pair finishes first."""
+    tail, split = _tail_plan(M, N, K)
+    assert tail > 0 and split in (2, 4)      # on a B200 (74 pairs) these shapes do take the split path
+    x, gm, W = orc.make_inputs(M, N, K, seed=M + N + K, gamma=has_gamma)
+    ref = orc.reference_fp32(x, gm, W, 1e-6)
+    y_split = run(x, gm, W, 1e-6)            # the default path
+    y_whole = run(x, gm, W, 1e-6, variant="prefill_pair_prestats_whole")
+    assert orc.rel_max_err(y_split, ref) <= BF16_TOL
+    assert orc.rel_max_err(y_whole, ref) <= BF16_TOL
+    assert orc.rel_max_err(y_split, y_whole.float()) <= ONE_ULP
+    for _ in range(3):
+        assert torch.equal(run(x, gm, W, 1e-6), y_split)
+    # the shared counters are back at zero: a small-M call on the same workspace is undisturbed
+    xs, gs, Ws = orc.make_inputs(8, 1024, 512, seed=3)
+    assert orc.rel_max_err(run(xs, gs, Ws, 1e-6), orc.reference_fp32(xs, gs, Ws, 1e-6)) <= BF16_TOL
+
+
+def test_tail_split_in_the_plain_gemm():
+    M, N, K = 768, 1280, 4096
+    assert _tail_plan(M, N, K)[1] >= 2
+    g = torch.Generator().manual_seed(5)
+    A = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    B = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16().to(DEV)
+    C = kb.gemm_nt(A, B)
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = A.float() @ B.float().t()
+    assert orc.rel_max_err(C, ref) <= BF16_TOL
+    assert torch.equal(kb.gemm_nt(A, B), C)
+
+
 def test_deterministic_and_workspace_reuse_across_shapes():
     """Back-to-back launches of different shapes share one workspace; results repeat bit for bit."""
     outs = {}
@@ -162,9 +214,13 @@ def test_config2_prefill_qkv():
     # size-independent properties
     y2 = kb.rmsnorm_linear(xd * 4, gd, Wd, 1e-6)                      # rms_norm is scale-invariant (eps aside)
     assert orc.rel_max_err(y2, y.float()) <= 5e-3                     # one bf16 ulp at max|y| is 3.9e-3
-    n0, n1 = 1536, 3072                                               # a column shard reproduces its columns exactly
-    ys = kb.rmsnorm_linear(xd, gd, Wd[n0:n1], 1e-6)
-    assert torch.equal(ys, y[:, n0:n1])
+    # a column shard reproduces its columns: bit for bit when every tile is computed whole, to one bf16 ulp when
+    # the tiles of the last round are summed in k-slices (which tiles those are depends on the shard's tile count)
+    n0, n1 = 1536, 3072
+    yw = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_prestats_whole")
+    assert torch.equal(kb.rmsnorm_linear(xd, gd, Wd[n0:n1], 1e-6, variant="prefill_pair_prestats_whole"), yw[:, n0:n1])
+    assert orc.rel_max_err(kb.rmsnorm_linear(xd, gd, Wd[n0:n1], 1e-6), y[:, n0:n1].float()) <= ONE_ULP
+    assert orc.rel_max_err(yw, y.float()) <= ONE_ULP
     assert torch.equal(kb.rmsnorm_linear(xd, gd, Wd, 1e-6), y)        # run-to-run identical
 
 
