@@ -109,6 +109,13 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
                            float eps, void* workspace, size_t workspace_bytes,
                            int variant, void* stream);
 
+/* Per-token statistics on their own: inv_rms[m] = rsqrt(mean_k x[m,k]^2 + eps) and, unless amax is NULL,
+ * amax[m] = max_k |x[m,k] * gamma[k]| (gamma NULL = ones).  These are what the fused kernels derive their
+ * epilogue scale (bf16 path) and their per-token quantisation step (FP8 path) from; the reference computes the
+ * first inside `F.rms_norm` (python/baselines/rmsnorm_swiglu.py:26) and has no counterpart for the second. */
+int rl_row_stats(const void* x, const void* gamma, float* inv_rms, float* amax,
+                 int M, int K, int64_t ldx, float eps, void* stream);
+
 /* The first kernel of the FP8 path on its own: per row, q = e4m3(x * gamma * 448 / amax) into
  * q [M, ldq] and row_scale[m] = rsqrt(mean x^2 + eps) * amax / 448.  No reference counterpart. */
 int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_scale,
@@ -153,6 +160,16 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
  * third_party/cublas_gemm/python/ext_kernel.cu:30-53).  `workspace` (>= 256 bytes) may be NULL. */
 int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
                  int64_t lda, int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream);
+
+/* LoRA-fused linear: y[M, N] = a[M, K] . b[N, K]^T + xa[M, L] . lb[N, L]^T in one pass (fp32 accumulation, one
+ * bf16 rounding), with xa = a . lA^T computed beforehand (rl_gemm_bf16 does) as the reference's fused kernels
+ * take it (`compiled_gemm(a_, b_, lxa, lB_, o)`, demo/new_profiling/lora_new.py:46-50; semantics `torch_lora`,
+ * python/baselines/lora.py:4-13).  The low-rank term rides as one more k-block of the main loop.
+ * L <= 64 and a multiple of 8; all leading dimensions multiples of 8. */
+int rl_lora_linear_bf16(const void* a, const void* b, const void* xa, const void* lb, void* y,
+                        int M, int N, int K, int L,
+                        int64_t lda, int64_t ldb, int64_t ldxa, int64_t ldlb, int64_t ldy,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* Self-test of the kernels' failure detection.  Launches one small CTA that waits on a barrier nothing
  * ever arrives on, with the given limit (<= 1 s); the wait must give up, record RL_ERR_DEVICE_TIMEOUT

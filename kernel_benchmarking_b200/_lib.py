@@ -52,10 +52,12 @@ SYMBOLS = [
     ("rl_workspace_init", _i, [_vp, _sz, _vp]),
     ("rl_rmsnorm_linear_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
     ("rl_rmsnorm_linear_fp8w", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
+    ("rl_row_stats", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _f, _vp]),
     ("rl_quantize_rows_e4m3", _i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _f, _vp]),
     ("rl_rmsnorm_linear_bf16_noalloc", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp]),
     ("rl_rmsnorm_swiglu_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _vp]),
     ("rl_gemm_bf16", _i, [_vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _vp, _sz, _vp]),
+    ("rl_lora_linear_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     ("rl_selftest_wait_timeout", _i, [_vp, _sz, ctypes.c_ulonglong, _vp]),
     ("rl_read_status", _i, [_vp, ctypes.POINTER(ctypes.c_int)]),
 ]

@@ -204,8 +204,9 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
 template <class Cfg>
 int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                         int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st,
-                        bool no_norm = false, size_t ws_bytes = 0, bool split_tail = true) {
-  CUtensorMap tx, tw, ty;
+                        bool no_norm = false, size_t ws_bytes = 0, bool split_tail = true, const void* x2 = nullptr,
+                        const void* w2 = nullptr, int L = 0, int64_t ldx2 = 0, int64_t ldw2 = 0) {
+  CUtensorMap tx, tw, ty, tx2, tw2;
   int rc;
   if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
   if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, ldw, 64,
@@ -213,6 +214,14 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
     return rc;
   if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
   if (Cfg::AMODE == A_SS_DIRECT && gamma != nullptr) return RL_ERR_BAD_VARIANT;
+  tx2 = tx;
+  tw2 = tw;
+  if (x2 != nullptr) {
+    // second operand pair [M, L] / [N, L]: same boxes as the first, columns L..63 come back as zeros
+    if (Cfg::AMODE != A_SS_DIRECT || Cfg::SWIGLU || L <= 0 || L > 64) return RL_ERR_BAD_VARIANT;
+    if ((rc = make_map(&tx2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x2, L, M, ldx2, 64, 128))) return rc;
+    if ((rc = make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w2, L, (uint64_t)N, ldw2, 64, Cfg::BN / 2))) return rc;
+  }
   PrefillParams p{};
   p.M = M; p.N = N; p.K = K; p.eps = eps;
   p.gamma = gamma;
@@ -220,6 +229,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   p.n_tiles = Cfg::SWIGLU ? (N + 127) / 128 : (N + Cfg::BN - 1) / Cfg::BN;  // SwiGLU: N = output channels, W has 2N rows
   p.group_m = 8;
   p.status = status;
+  p.extra_kb = (x2 != nullptr) ? 1 : 0;
   if (Cfg::PRESTATS && !no_norm) {
     if (status == nullptr) return RL_ERR_WORKSPACE;
     float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + ws_layout(M > 65 ? M : 65, N).rstd_off);
@@ -257,7 +267,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
   int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
   if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && split_tail && status != nullptr) {
     const WsLayout wl = ws_layout(M > 65 ? M : 65, N);
-    const TailPlan tp = plan_tail(tiles, max_pairs, (K + 63) / 64);
+    const TailPlan tp = plan_tail(tiles, max_pairs, (K + 63) / 64 + p.extra_kb);
     if (tp.split > 1 && ws_bytes >= wl.total) {
       p.tail_tiles = tp.tiles;
       p.tail_split = tp.split;
@@ -279,10 +289,10 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    e = cudaLaunchKernelEx(&lc, prefill_pair_kernel<Cfg>, tx, tw, ty, p);
+    e = cudaLaunchKernelEx(&lc, prefill_pair_kernel<Cfg>, tx, tw, ty, tx2, tw2, p);
     return e == cudaSuccess ? RL_OK : cuda_err(e);
   }
-  prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, p);
+  prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, tx2, tw2, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
@@ -558,6 +568,18 @@ int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_
   return launch_rowquant(x, gamma, q, row_scale, M, K, ldx, ldq, eps, (cudaStream_t)stream);
 }
 
+int rl_row_stats(const void* x, const void* gamma, float* inv_rms, float* amax, int M, int K, int64_t ldx, float eps,
+                 void* stream) {
+  if (!x || !inv_rms) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || K <= 0 || ldx < K) return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (ldx & 7) || !aligned16(x) || (gamma && !aligned16(gamma))) return RL_ERR_ALIGNMENT;
+  rowstats_amax_kernel<<<M, 128, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                                            reinterpret_cast<const __nv_bfloat16*>(gamma), inv_rms, amax, M,
+                                                            K, ldx, eps);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? RL_OK : cuda_err(e);
+}
+
 int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, const float* w_scale, void* y, int M, int N,
                            int K, int64_t ldx, int64_t ldw, int64_t ldy, float eps, void* workspace,
                            size_t workspace_bytes, int variant, void* stream) {
@@ -641,6 +663,25 @@ int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
       A, nullptr, B, C, M, N, K, lda, ldb, ldc, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
       /*no_norm=*/true, workspace_bytes);
+}
+
+int rl_lora_linear_bf16(const void* a, const void* b, const void* xa, const void* lb, void* y, int M, int N, int K, int L,
+                        int64_t lda, int64_t ldb, int64_t ldxa, int64_t ldlb, int64_t ldy, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!a || !b || !xa || !lb || !y) return RL_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || L <= 0 || L > 64 || lda < K || ldb < K || ldxa < L || ldlb < L || ldy < N)
+    return RL_ERR_BAD_SHAPE;
+  if ((K & 7) || (L & 7) || (lda & 7) || (ldb & 7) || (ldxa & 7) || (ldlb & 7) || (ldy & 7) || !aligned16(a) ||
+      !aligned16(b) || !aligned16(xa) || !aligned16(lb) || !aligned16(y))
+    return RL_ERR_ALIGNMENT;
+  if (workspace && workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
+      a, nullptr, b, y, M, N, K, lda, ldb, ldy, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
+      /*no_norm=*/true, workspace_bytes, /*split_tail=*/true, xa, lb, L, ldxa, ldlb);
 }
 
 int rl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream) {

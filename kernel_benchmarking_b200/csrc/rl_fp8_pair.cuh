@@ -91,6 +91,39 @@ __global__ void __launch_bounds__(128) rowquant_kernel(const RowQuantParams p) {
   if (threadIdx.x == 0) p.row_scale[m] = (1.0f / sqrtf(ssq / (float)p.K + p.eps)) * (amax / 448.0f);
 }
 
+// The statistics pass of rowquant_kernel on its own: inv_rms[m] = rsqrt(mean_k x^2 + eps) and, when asked for,
+// amax[m] = max_k |x * gamma| (the fp32 product of the two bf16 values, which is exact).
+__global__ void __launch_bounds__(128) rowstats_amax_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gamma,
+                                                            float* __restrict__ inv_rms, float* __restrict__ amax_out,
+                                                            int M, int K, long long ldx, float eps) {
+  __shared__ float scratch[4];
+  const int m = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)m * ldx);
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  const int chunks = K >> 3;
+  float ssq = 0.f, amax = 0.f;
+  for (int c = threadIdx.x; c < chunks; c += 128) {
+    const uint4 u = xr[c];
+    uint4 g = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 ones
+    if (gr != nullptr) g = __ldg(gr + c);
+    const uint32_t xs[4] = {u.x, u.y, u.z, u.w}, gs[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x0 = bf16lo(xs[i]), x1 = bf16hi(xs[i]);
+      ssq = fmaf(x0, x0, ssq);
+      ssq = fmaf(x1, x1, ssq);
+      amax = fmaxf(amax, fmaxf(fabsf(x0 * bf16lo(gs[i])), fabsf(x1 * bf16hi(gs[i]))));
+    }
+  }
+  ssq = block_reduce_128(ssq, false, scratch);
+  amax = block_reduce_128(amax, true, scratch);
+  if (threadIdx.x == 0) {
+    inv_rms[m] = 1.0f / sqrtf(ssq / (float)K + eps);
+    if (amax_out != nullptr) amax_out[m] = amax;
+  }
+}
+
 // ---------------------------------------------------------------- FP8 pair GEMM
 struct Fp8GemmParams {
   int M, N, K;

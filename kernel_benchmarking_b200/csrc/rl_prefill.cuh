@@ -36,6 +36,7 @@ struct PrefillParams {
   int tail_tiles, tail_split;
   unsigned* tail_counters;
   float* tail_partials;
+  int extra_kb;  // pair kernels: k-blocks appended from a second pair of operand matrices (0 or 1)
 };
 
 // Row statistics on their own: rstd[m] = rsqrt(mean_k x[m,k]^2 + eps).  One warp per token row, 16-byte

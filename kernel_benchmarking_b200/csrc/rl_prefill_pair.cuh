@@ -120,7 +120,8 @@ __device__ __forceinline__ bool pair_item(const PrefillParams& p, int pair, int 
 template <class Cfg>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::THREADS, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                    const __grid_constant__ CUtensorMap tm_y, const PrefillParams p) {
+                    const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_x2,
+                    const __grid_constant__ CUtensorMap tm_w2, const PrefillParams p) {
   constexpr int BN = Cfg::BN, NACC = Cfg::NACC, STAGES = Cfg::STAGES, ASLOTS = Cfg::ASLOTS, TG = Cfg::TG;
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
   constexpr bool PRESTATS = Cfg::PRESTATS;
@@ -152,7 +153,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
   const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
-  const int KB = (p.K + 63) >> 6;
+  // p.extra_kb k-blocks are appended to every tile's k-loop with their operands taken from a second pair of
+  // matrices (tm_x2 [M, L], tm_w2 [N, L], columns beyond L zero-filled by TMA): y = x W^T + x2 W2^T, the low-rank
+  // update of a LoRA layer riding in the same accumulator.  Only the producer knows the difference.
+  const int KB_main = (p.K + 63) >> 6;
+  const int KB = KB_main + p.extra_kb;
   const int total_tiles = p.m_tiles * p.n_tiles;  // 256 x BN tiles
   const bool has_gamma = (p.gamma != nullptr);
 
@@ -176,6 +181,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     prefetch_tmap(&tm_x);
     prefetch_tmap(&tm_w);
     prefetch_tmap(&tm_y);
+    if (p.extra_kb) {
+      prefetch_tmap(&tm_x2);
+      prefetch_tmap(&tm_w2);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -202,14 +211,17 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
         if (elect_one()) {
           RL_STAMP(0, jp);
+          const bool extra = (kb >= KB_main);
           const int kvalid = min(64, p.K - kb * 64);
-          const uint32_t gbytes = (TS && has_gamma) ? (uint32_t)kvalid * 2u : 0u;
+          const uint32_t gbytes = (TS && has_gamma && !extra) ? (uint32_t)kvalid * 2u : 0u;
+          const int kcol = extra ? (kb - KB_main) * 64 : kb * 64;
           mbar_expect_tx(bar_fullA(s), Cfg::A_BYTES + gbytes);
-          tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, &tm_x, bar_fullA(s), kb * 64, mt * 256 + (int)rank * 128);
+          tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, extra ? &tm_x2 : &tm_x, bar_fullA(s), kcol,
+                      mt * 256 + (int)rank * 128);
           if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_fullA(s));
           const uint32_t lead_ready = lead_ready0 + 8u * s;
           mbar_expect_tx_cluster(lead_ready, Cfg::B_BYTES);
-          tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kb * 64,
+          tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, extra ? &tm_w2 : &tm_w, lead_ready, kcol,
                            SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
         }
         __syncwarp();

@@ -197,11 +197,39 @@ def rmsnorm_linear_job(config: int, seed: int = 18) -> ProfilingJob:
                         ref_by_kernel={"max": ref_gemm, "max_b200": ref_gemm})
 
 
+LORA_DIM = 16   # demo/new_profiling/lora_new.py:19
+
+
+def lora_job(config: int, seed: int = 18) -> ProfilingJob:
+    """The job of demo/new_profiling/lora_new.py for shape `config` (`LORA_NT_16`, python/workload_shapes.py:56-63:
+    X [m, k], W [n, k], A [16, k], B [n, 16]) with `b200` (this library's fused kernel), `torch` (the reference's
+    eager expression, the baseline) and `max` (the plain matmul without the low-rank term)."""
+    from .ops import gemm_nt, lora_linear
+    if not 0 <= config < len(RMSNORM_LINEAR_SHAPES):
+        raise IndexError(f"config must be in [0, {len(RMSNORM_LINEAR_SHAPES)})")
+    m, n, k = RMSNORM_LINEAR_SHAPES[config]
+    g = torch.Generator().manual_seed(seed)
+    x, w, la, lb = (normal_bernoulli(shape, generator=g).to(torch.bfloat16).cuda()
+                    for shape in ((m, k), (n, k), (LORA_DIM, k), (n, LORA_DIM)))
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+    def torch_kernel(a, b, lA, lB):   # python/baselines/lora.py:4-13
+        return (a @ b.t()) + ((a @ lA.t()) @ lB.t())
+
+    kernels = {"b200": lora_linear, "torch": torch_kernel, "max": lambda a, b: a @ b.t(),
+               "max_b200": lambda a, b: gemm_nt(a, b)}
+    masks = {"b200": (0, 1, 2, 3), "torch": (0, 1, 2, 3), "max": (0, 1), "max_b200": (0, 1)}
+    ref_gemm = x.double() @ w.double().t()
+    return ProfilingJob("lora", config, (m, n, k), kernels, (x, w, la, lb, out), masks, baseline="torch", ref="torch",
+                        ref_by_kernel={"max": ref_gemm, "max_b200": ref_gemm})
+
+
 def main(argv=None) -> None:
-    """`python -m kernel_benchmarking_b200.harness CONFIG [--ncu] [--csv FILE]` - the new-style CLI of the
-    reference (profile_utils.py:444-456); `--header` prints the CSV header (demo/gen_header.py)."""
+    """`python -m kernel_benchmarking_b200.harness CONFIG [--workload rmsnorm_linear|lora] [--ncu] [--csv FILE]` - the
+    new-style CLI of the reference (profile_utils.py:444-456); `--header` prints the CSV header (demo/gen_header.py)."""
     ap = argparse.ArgumentParser(description=main.__doc__)
     ap.add_argument("config", type=int, nargs="?", default=0)
+    ap.add_argument("--workload", default="rmsnorm_linear", choices=["rmsnorm_linear", "lora"])
     ap.add_argument("--ncu", action="store_true")
     ap.add_argument("--csv", default=None)
     ap.add_argument("--header", action="store_true")
@@ -209,7 +237,8 @@ def main(argv=None) -> None:
     if ns.header:
         print(ExperimentRow.header())
         return
-    write_rows(rmsnorm_linear_job(ns.config).run(ncu=ns.ncu), ns.csv)
+    job = lora_job(ns.config) if ns.workload == "lora" else rmsnorm_linear_job(ns.config)
+    write_rows(job.run(ncu=ns.ncu), ns.csv)
 
 
 if __name__ == "__main__":

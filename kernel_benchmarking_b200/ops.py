@@ -189,6 +189,42 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = N
     return out
 
 
+def lora_linear(a: torch.Tensor, b: torch.Tensor, lA: torch.Tensor, lB: torch.Tensor, *,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K] @ b [N, K].t() + (a @ lA [L, K].t()) @ lB [N, L].t(): the reference's `torch_lora`
+    (python/baselines/lora.py:4-13).  As in its fused kernels (demo/new_profiling/lora_new.py:44-50) the narrow
+    product a @ lA.t() is computed first (here by this library's own GEMM) and rounded to bf16; the second kernel
+    adds the low-rank term inside the main GEMM's accumulator.  L <= 64, a multiple of 8."""
+    for name, t in (("a", a), ("b", b), ("lA", lA), ("lB", lB)):
+        _check_matrix(name, t, torch.bfloat16)
+    M, K = a.shape
+    N, L = lB.shape
+    if b.shape != (N, K) or lA.shape != (L, K) or any(t.device != a.device for t in (b, lA, lB)):
+        raise ValueError("expected a [M, K], b [N, K], lA [L, K], lB [N, L] on one device")
+    if L > 64 or L % 8:
+        raise ValueError(f"lora_dim must be a multiple of 8 and at most 64, got {L}")
+    if out is None:
+        ldy = (N + 7) // 8 * 8
+        buf = torch.empty((M, ldy), dtype=torch.bfloat16, device=a.device)
+        out = buf if ldy == N else buf[:, :N]
+    else:
+        _check_matrix("out", out, torch.bfloat16)
+        if tuple(out.shape) != (M, N) or out.device != a.device:
+            raise ValueError(f"out must be [{M}, {N}] on a's device")
+    if M == 0 or N == 0:
+        return out
+    xa = gemm_nt(a, lA)
+    lib = _lib.load()
+    stream = _stream_ptr(a.device)
+    with _on_device(a.device):
+        ws = _workspace(a.device, lib.rl_workspace_bytes(max(M, 65), N, K, _lib.RL_W_BF16), stream)
+        rc = lib.rl_lora_linear_bf16(a.data_ptr(), b.data_ptr(), xa.data_ptr(), lB.data_ptr(), out.data_ptr(), M, N, K, L,
+                                     a.stride(0), b.stride(0), xa.stride(0), lB.stride(0), out.stride(0),
+                                     ws.data_ptr(), ws.numel(), stream)
+    _lib.check(rc, "rl_lora_linear_bf16")
+    return out
+
+
 def quantize_rows_e4m3(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float = 1e-6):
     """First kernel of the FP8 path on its own: returns (q [M, K] float8_e4m3fn, row_scale [M] fp32) with
     q = e4m3(x * gamma * 448 / amax_row) and row_scale = rsqrt(mean x^2 + eps) * amax_row / 448."""
@@ -202,6 +238,25 @@ def quantize_rows_e4m3(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: floa
                                                _stream_ptr(x.device))
     _lib.check(rc, "rl_quantize_rows_e4m3")
     return q.view(torch.float8_e4m3fn), rs
+
+
+def row_stats(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float = 1e-6, *, want_amax: bool = True):
+    """Per-token statistics: (inv_rms [M] fp32 = rsqrt(mean x^2 + eps), amax [M] fp32 = max |x * gamma| or None)."""
+    _check_matrix("x", x, torch.bfloat16)
+    M, K = x.shape
+    if gamma is not None and (gamma.dtype != torch.bfloat16 or gamma.device != x.device or gamma.shape != (K,)
+                              or gamma.stride(0) != 1):
+        raise ValueError(f"gamma must be a contiguous bf16 vector of length K={K} on x's device")
+    inv_rms = torch.empty((M,), dtype=torch.float32, device=x.device)
+    amax = torch.empty((M,), dtype=torch.float32, device=x.device) if want_amax else None
+    if M == 0:
+        return inv_rms, amax
+    with _on_device(x.device):
+        rc = _lib.load().rl_row_stats(x.data_ptr(), None if gamma is None else gamma.data_ptr(), inv_rms.data_ptr(),
+                                      None if amax is None else amax.data_ptr(), M, K, x.stride(0), ctypes.c_float(eps),
+                                      _stream_ptr(x.device))
+    _lib.check(rc, "rl_row_stats")
+    return inv_rms, amax
 
 
 def check_status(device: Optional[torch.device] = None) -> None:

@@ -61,6 +61,12 @@ def torch_rmsnorm_swiglu(a: torch.Tensor, gamma: torch.Tensor | None, bb1: torch
     return torch.nn.functional.silu(o1) * o2
 
 
+def torch_lora(a: torch.Tensor, b: torch.Tensor, lA: torch.Tensor, lB: torch.Tensor) -> torch.Tensor:
+    """python/baselines/lora.py:4-13 (`torch_lora`): a [m, k], b [n, k], lA [l, k], lB [n, l], everything k-major;
+    (a @ b.t()) + ((a @ lA.t()) @ lB.t())."""
+    return (a @ b.t()) + ((a @ lA.t()) @ lB.t())
+
+
 def reference_fp32(x: torch.Tensor, gamma: torch.Tensor | None, W: torch.Tensor, eps: float,
                    w_scale: torch.Tensor | None = None, dtype=torch.float32) -> torch.Tensor:
     """The parity target for the GPU kernels: inputs (bf16 / e4m3 bit patterns as

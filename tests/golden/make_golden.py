@@ -5,8 +5,9 @@ Run on a machine that has the reference checkout (pure torch on CPU):
     python tests/golden/make_golden.py /path/to/reference
 
 It imports the reference's `baselines.rmsnorm_swiglu` (python/baselines/
-rmsnorm_swiglu.py:25-34) and `RMSNormLinearModule` (python/baselines/
-rmsnorm_swiglu_trt.py:7-21), feeds them seeded inputs and stores inputs and
+rmsnorm_swiglu.py:25-34), `RMSNormLinearModule` (python/baselines/
+rmsnorm_swiglu_trt.py:7-21) and `baselines.lora.torch_lora` (python/baselines/
+lora.py:4-13), feeds them seeded inputs and stores inputs and
 outputs in one compressed .npz per case.  bf16 tensors are stored as uint16 bit
 patterns, e4m3 as uint8 codes.  The reference operator has no gamma; cases with
 gamma call the reference on (x, W * gamma[None, :]) in fp64, which is the same
@@ -112,6 +113,20 @@ def main(ref_root: str) -> None:
         os.path.join(HERE, "swiglu_bf16_48x128x192.npz"),
         x_bits=bf16_bits(x), W_bits=bf16_bits(bb1), eps=np.float64(1e-5),
         y_ref_fp64=ref_rmsnorm_swiglu(x.double(), bb1.double(), 1e-5).float().numpy(),
+    )
+    # ---- case 7: LoRA-fused linear, lora_dim 16 (its own seed: independent of the cases above) ----
+    from baselines.lora import torch_lora as ref_lora  # noqa: E402
+    torch.manual_seed(1818)
+    M, N, K, L = 64, 136, 192, 16
+    a = torch.randn(M, K).to(torch.bfloat16)
+    b = (torch.randn(N, K) * K ** -0.5).to(torch.bfloat16)
+    lA = (torch.randn(L, K) * K ** -0.5).to(torch.bfloat16)
+    lB = (torch.randn(N, L) * L ** -0.5).to(torch.bfloat16)
+    np.savez_compressed(
+        os.path.join(HERE, "lora_bf16_64x136x192_l16.npz"),
+        a_bits=bf16_bits(a), b_bits=bf16_bits(b), lA_bits=bf16_bits(lA), lB_bits=bf16_bits(lB),
+        y_ref_fp64=ref_lora(a.double(), b.double(), lA.double(), lB.double()).float().numpy(),
+        y_ref_bf16_bits=bf16_bits(ref_lora(a, b, lA, lB)),
     )
     print("golden vectors written to", HERE)
 

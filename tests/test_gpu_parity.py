@@ -307,6 +307,21 @@ def test_row_quantisation_is_bit_exact(M, K, has_gamma):
     torch.testing.assert_close(rs.cpu(), rs_ref, rtol=2e-6, atol=0)
 
 
+@pytest.mark.parametrize("M,K,has_gamma", [(1, 64, True), (37, 256, False), (300, 4096, True), (4096, 8192, True)])
+def test_row_statistics(M, K, has_gamma):
+    """inv_rms to fp32 summation order, amax exactly (a product of two bf16 values is exact in fp32)."""
+    x, gm, _ = orc.make_inputs(M, 8, K, seed=K + M, gamma=has_gamma)
+    inv_rms, amax = kb.row_stats(x.to(DEV), None if gm is None else gm.to(DEV), 1e-6)
+    torch.cuda.synchronize()
+    x32 = x.float()
+    ref_rms = torch.rsqrt(x32.double().pow(2).mean(dim=1) + 1e-6).float()
+    ref_amax = (x32 * (gm.float() if gm is not None else 1.0)).abs().amax(dim=1)
+    assert torch.allclose(inv_rms.cpu(), ref_rms, rtol=2e-6, atol=0)
+    assert torch.equal(amax.cpu(), ref_amax)
+    only_rms, none = kb.row_stats(x.to(DEV), None if gm is None else gm.to(DEV), 1e-6, want_amax=False)
+    assert none is None and torch.equal(only_rms, inv_rms)
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 2048), (1000, 1032, 4096), (5, 264, 1024)])
 def test_fp8_shapes(M, N, K):
     x, gm, W = orc.make_inputs(M, N, K, seed=M + N)
@@ -414,6 +429,35 @@ def test_swiglu_golden_and_shapes(golden_dir):
         assert orc.rel_max_err(y.cpu(), ref) <= BF16_TOL
     with pytest.raises(ValueError):
         kb.rmsnorm_swiglu(x.to(DEV), gm.to(DEV), W[:200].contiguous().to(DEV), 1e-6)   # n not a multiple of 128
+
+
+def test_lora_golden_and_shapes(golden_dir):
+    """LoRA-fused linear (the low-rank term as one more k-block of the main loop) against the reference's
+    `torch_lora` output and, on larger shapes, against the restatement in fp32 on the GPU."""
+    g = np.load(os.path.join(golden_dir, "lora_bf16_64x136x192_l16.npz"))
+    a, b, lA, lB = (bf16(g[k]).to(DEV) for k in ("a_bits", "b_bits", "lA_bits", "lB_bits"))
+    y = kb.lora_linear(a, b, lA, lB)
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert orc.rel_max_err(y.cpu(), torch.from_numpy(g["y_ref_fp64"])) <= BF16_TOL
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for (M, N, K, L) in [(300, 520, 320, 16), (2048, 2048, 2048, 16), (4096, 1024, 4096, 16), (512, 1024, 4096, 64),
+                         (1024, 768, 1000, 8)]:
+        gen = torch.Generator().manual_seed(M + N + K + L)
+        a = torch.randn(M, K, generator=gen).bfloat16().to(DEV)
+        b = (torch.randn(N, K, generator=gen) * K ** -0.5).bfloat16().to(DEV)
+        lA = (torch.randn(L, K, generator=gen) * K ** -0.5).bfloat16().to(DEV)
+        lB = torch.randn(N, L, generator=gen).bfloat16().to(DEV)      # a low-rank term as large as the main one
+        y = kb.lora_linear(a, b, lA, lB)
+        torch.cuda.synchronize()
+        kb.check_status()
+        ref = orc.torch_lora(a.float(), b.float(), lA.float(), lB.float())
+        assert orc.rel_max_err(y, ref) <= BF16_TOL, (M, N, K, L)
+        # the low-rank term really is in there
+        assert orc.rel_max_err(kb.gemm_nt(a, b), ref) > 5 * BF16_TOL
+        assert torch.equal(kb.lora_linear(a, b, lA, lB), y)
+    with pytest.raises(ValueError):
+        kb.lora_linear(a, b, lA[:4], lB[:, :4].contiguous())         # lora_dim 4: not a multiple of 8
 
 
 def test_bounded_wait_reports_instead_of_hanging():

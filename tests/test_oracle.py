@@ -140,3 +140,17 @@ def test_swiglu_golden(golden_dir):
     n = h.shape[1] // 2
     y_np = h[:, :n] / (1.0 + np.exp(-h[:, :n])) * h[:, n:]
     np.testing.assert_allclose(y_np.astype(np.float32), g["y_ref_fp64"], rtol=1e-5, atol=1e-6)
+
+
+def test_lora_golden(golden_dir):
+    """The LoRA restatement against the reference's own `torch_lora` output (fp64 run and its bf16 run)."""
+    g = load(golden_dir, "lora_bf16_64x136x192_l16.npz")
+    a, b, lA, lB = (bf16(g[k]) for k in ("a_bits", "b_bits", "lA_bits", "lB_bits"))
+    y = orc.torch_lora(a.double(), b.double(), lA.double(), lB.double())
+    np.testing.assert_allclose(y.float().numpy(), g["y_ref_fp64"], rtol=1e-6, atol=1e-6)
+    assert torch.equal(orc.torch_lora(a, b, lA, lB), bf16(g["y_ref_bf16_bits"]))
+    # numpy restatement in fp64
+    f = orc.bf16_bits_to_f32
+    a64, b64, lA64, lB64 = (f(g[k]).astype(np.float64) for k in ("a_bits", "b_bits", "lA_bits", "lB_bits"))
+    y_np = a64 @ b64.T + (a64 @ lA64.T) @ lB64.T
+    np.testing.assert_allclose(y_np.astype(np.float32), g["y_ref_fp64"], rtol=1e-6, atol=1e-6)
