@@ -186,6 +186,34 @@ int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, voi
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+// How many CTA pairs of this kernel the device holds at once (the two CTAs of a pair sit on neighbouring SMs of
+// one TPC, so this can be fewer than SMs / 2).  Asked once per device and kernel.
+template <class Cfg>
+int max_cta_pairs(int sms, int* out) {
+  static int cache[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int n = cache[dev & 63];
+  if (n == 0) {
+    cudaError_t e = set_smem_once(prefill_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_err(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sms / 2));
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    e = cudaOccupancyMaxActiveClusters(&n, prefill_pair_kernel<Cfg>, &cfg);
+    if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / 2; }
+    cache[dev & 63] = n;
+  }
+  *out = n;
+  return RL_OK;
+}
+
 // What to do with the last, partly filled round of tiles.  `tiles` tiles are dealt to `max_pairs` CTA pairs; r =
 // tiles % max_pairs of them form the last round, which costs a whole tile's time however few they are.  Cut
 // along K into S slices, r * S pairs share that work and then spend a few microseconds exchanging partial
@@ -242,27 +270,8 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
 #endif
   cudaError_t e = set_smem_once(prefill_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
-  // how many CTA pairs the device can hold at once (pairs must sit on neighbouring SMs)
-  static int max_pairs_cache[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  int max_pairs = max_pairs_cache[dev & 63];
-  if (max_pairs == 0) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (sms / 2));
-    cfg.blockDim = dim3(Cfg::THREADS);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, prefill_pair_kernel<Cfg>, &cfg);
-    if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / 2; }
-    max_pairs = n;
-    max_pairs_cache[dev & 63] = n;
-  }
+  int max_pairs = 0;
+  if ((rc = max_cta_pairs<Cfg>(sms, &max_pairs))) return rc;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
   if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && split_tail && status != nullptr) {
@@ -527,13 +536,23 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
 
   // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
   if (variant == RL_VARIANT_AUTO) {
-    // with a workspace the pair kernel takes 1/rms from the (overlapped) row-statistics pass; without one it
-    // accumulates the sums of squares itself
-    // and without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
-    // which frees tensor memory for a second accumulator
-    variant = (M > 128) ? (workspace ? (g ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS)
-                                     : RL_VARIANT_PREFILL_PAIR_N256)
-                        : RL_VARIANT_PREFILL_TS_N192;
+    if (M <= 128) {
+      variant = RL_VARIANT_PREFILL_TS_N192;
+    } else {
+      // Without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
+      // which frees tensor memory for a second accumulator.
+      // Row statistics: from the overlapped pre-pass when there is a workspace and more than one round of tiles
+      // (or few enough tiles that their k-loops get split): every column tile would otherwise recompute the same
+      // sums on warps that share schedulers with the MMA warp.  With one round, not split, the pre-pass only adds
+      // a second read of x and a launch in front of an epilogue that has to wait for it (12-15 % at K >= 4096):
+      // there the transform warps accumulate the sums themselves.
+      int pairs = di.sms / 2;
+      (void)max_cta_pairs<PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true>>(di.sms, &pairs);
+      const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+      const bool one_round = tiles <= pairs && 2 * tiles > pairs;
+      if (!workspace || one_round) variant = g ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_PAIR_DIRECT;
+      else variant = g ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
+    }
   }
   const bool split_tail = (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
 #define RL_PREFILL(BN, ST, AM, TG) \

@@ -247,7 +247,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1u, ctl, 1, 2 * STAGES + 2 + acc, it)) break;
         const uint32_t d = tmem_base + acc * BN;
-        uint32_t ready_now = mbar_try_wait(bar_ready(s), ph);
+        uint32_t ready_now = mbar_test_wait(bar_ready(s), ph);
         for (int kb = 0; kb < KB; ++kb) {
           if (!ready_now) {
             if (!mbar_wait(bar_ready(s), ph, ctl, 1, s, kb)) { ok = false; break; }
@@ -255,7 +255,7 @@ fp8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           tc_fence_after();
           const int sn = (s + 1 == STAGES) ? 0 : s + 1;
           const uint32_t phn = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
-          ready_now = mbar_try_wait(bar_ready(sn), phn);
+          ready_now = mbar_test_wait(bar_ready(sn), phn);
           umma_kblock_f8_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
                                  bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != 0), bar_empty(s),
                                  leader);

@@ -42,7 +42,18 @@ namespace rl {
       p.trace[((int)rank * 8 + (ev)) * RL_TRACE_N + (idx)] = clock64();                 \
   } while (0)
 #define RL_DEBUG(bit) ((p.debug & (bit)) != 0)
+// wall-clock (ns) stamps of the kernel's phases, CTA 0 only, behind the clock64 stamps
+#define RL_GSTAMP(i)                                                                         \
+  do {                                                                                       \
+    if (p.trace != nullptr && blockIdx.x == 0) {                                             \
+      p.trace[2 * 8 * RL_TRACE_N + (i)] = (long long)global_timer_ns();                      \
+      p.trace[2 * 8 * RL_TRACE_N + 8 + (i)] = clock64();                                     \
+    }                                                                                        \
+  } while (0)
 #else
+#define RL_GSTAMP(i) \
+  do {               \
+  } while (0)
 #define RL_STAMP(ev, idx) \
   do {                    \
   } while (0)
@@ -131,6 +142,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
+  if (threadIdx.x == 0) RL_GSTAMP(0);
   if (sbase & 1023u) {
     // swizzled tiles need a 1024-byte aligned base; every thread of both CTAs sees the same value
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)DEV_BAD_SMEM_ALIGNMENT);
@@ -195,6 +207,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) RL_GSTAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
@@ -240,6 +253,33 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       uint32_t ph = 0;
       bool ok = true;
       PairItem w;
+#ifdef RL_TRACE
+      if (RL_DEBUG(1024)) {
+        // experiment: one throw-away pair MMA right after set-up, committed to the (otherwise unused until the
+        // tail) scratch barrier of this CTA only; when does it complete?
+        if (lane == 0) {
+          if (TS) umma_ts_pair(tmem_base, tmem_base + Cfg::A_COL0, bdesc0, idesc, 0u);
+          else umma_ss_pair(tmem_base, adesc0, bdesc0, idesc, 0u);
+          if (RL_DEBUG(2048)) umma_commit_pair(bar_tail, (uint16_t)3);   // multicast form
+          else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_tail) : "memory");
+          RL_GSTAMP(6);
+          while (!mbar_try_wait(bar_tail, 0u)) {}
+          RL_GSTAMP(7);
+        }
+        __syncwarp();
+      }
+      if (RL_DEBUG(256)) {
+        // experiment: wake the tensor pipe with throw-away MMAs while the first operands are still in flight
+        const int n_warm = (p.debug >> 12) & 0xff;
+        for (int i = 0; i < n_warm; ++i) {
+          if (lane == 0) {
+            if (TS) umma_ts_pair(tmem_base, tmem_base + Cfg::A_COL0, bdesc0, idesc, 0u);
+            else umma_ss_pair(tmem_base, adesc0, bdesc0, idesc, 0u);
+          }
+          __syncwarp();
+        }
+      }
+#endif
       for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
         const int acc = (NACC == 2) ? (it & 1) : 0;
         const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
@@ -248,16 +288,18 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const uint32_t d = tmem_base + acc * BN;
         // The issue loop sets the tensor cores' pace: one barrier wait per k-block, the poll for the
         // next slot started before this slot's MMAs are issued, and one predicated issue block.
-        uint32_t ready_now = mbar_try_wait(bar_ready(s), ph);
+        uint32_t ready_now = mbar_test_wait(bar_ready(s), ph);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (RL_DEBUG(4096) && it == 0 && kb == w.kb0) ready_now = 1u;  // experiment: first k-block issued on whatever is there
           if (!ready_now) {
             if (!mbar_wait(bar_ready(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
           }
           if (lane == 0) RL_STAMP(2, it * KB + kb - w.kb0);
+          if (lane == 0 && it == 0 && kb == w.kb0) RL_GSTAMP(2);
           tc_fence_after();
           const int sn = (s + 1 == STAGES) ? 0 : s + 1;
           const uint32_t phn = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
-          ready_now = mbar_try_wait(bar_ready(sn), phn);  // next k-block (or the next tile's first)
+          ready_now = mbar_test_wait(bar_ready(sn), phn);  // next k-block (or the next tile's first)
           if (TS) {
             umma_kblock_ts_pair(d, tmem_base + Cfg::A_COL0 + aslot * 32, bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)),
                                 idesc, (uint32_t)(kb != w.kb0), bar_empty(s), leader);
@@ -272,6 +314,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
         ok = __all_sync(0xffffffffu, ok);
         if (ok) umma_commit_pair_pred(bar_tfull(acc), leader);
+#ifdef RL_TRACE
+        if (RL_DEBUG(512) && it == 0) {  // experiment: when does the issuing warp itself see the accumulator complete?
+          const uint32_t aph0 = 0u;
+          while (!mbar_try_wait(bar_tfull(acc), aph0)) {}
+          if (lane == 0) RL_GSTAMP(6);
+        }
+#endif
       }
     }
     __syncwarp();
@@ -675,7 +724,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
       }
     }
+    if (epi_tid == 0) RL_GSTAMP(3);
     if (epi_tid == 0) tma_store_wait_all<0>();
+    if (epi_tid == 0) RL_GSTAMP(4);
   }
 
   // ------------------------------------------------------------ teardown
@@ -691,6 +742,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
+  if (threadIdx.x == 32) RL_GSTAMP(5);
 }
 
 }  // namespace rl

@@ -56,6 +56,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Non-blocking form.  mbarrier.try_wait may suspend the thread until the phase completes or a hardware time
+// limit (several microseconds here) runs out, which is what a waiter wants but not what a look-ahead poll
+// wants: a poll of a barrier that is not about to complete must come straight back.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Wait limit: far longer than any legitimate wait inside these kernels (the
 // longest kernel runs tens of milliseconds), short enough that a protocol bug
 // ends the launch instead of hanging the GPU.
