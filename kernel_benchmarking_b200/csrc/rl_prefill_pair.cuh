@@ -253,33 +253,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       uint32_t ph = 0;
       bool ok = true;
       PairItem w;
-#ifdef RL_TRACE
-      if (RL_DEBUG(1024)) {
-        // experiment: one throw-away pair MMA right after set-up, committed to the (otherwise unused until the
-        // tail) scratch barrier of this CTA only; when does it complete?
-        if (lane == 0) {
-          if (TS) umma_ts_pair(tmem_base, tmem_base + Cfg::A_COL0, bdesc0, idesc, 0u);
-          else umma_ss_pair(tmem_base, adesc0, bdesc0, idesc, 0u);
-          if (RL_DEBUG(2048)) umma_commit_pair(bar_tail, (uint16_t)3);   // multicast form
-          else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_tail) : "memory");
-          RL_GSTAMP(6);
-          while (!mbar_try_wait(bar_tail, 0u)) {}
-          RL_GSTAMP(7);
-        }
-        __syncwarp();
-      }
-      if (RL_DEBUG(256)) {
-        // experiment: wake the tensor pipe with throw-away MMAs while the first operands are still in flight
-        const int n_warm = (p.debug >> 12) & 0xff;
-        for (int i = 0; i < n_warm; ++i) {
-          if (lane == 0) {
-            if (TS) umma_ts_pair(tmem_base, tmem_base + Cfg::A_COL0, bdesc0, idesc, 0u);
-            else umma_ss_pair(tmem_base, adesc0, bdesc0, idesc, 0u);
-          }
-          __syncwarp();
-        }
-      }
-#endif
       for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
         const int acc = (NACC == 2) ? (it & 1) : 0;
         const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
@@ -290,7 +263,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         // next slot started before this slot's MMAs are issued, and one predicated issue block.
         uint32_t ready_now = mbar_test_wait(bar_ready(s), ph);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (RL_DEBUG(4096) && it == 0 && kb == w.kb0) ready_now = 1u;  // experiment: first k-block issued on whatever is there
           if (!ready_now) {
             if (!mbar_wait(bar_ready(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
           }
@@ -314,13 +286,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
         ok = __all_sync(0xffffffffu, ok);
         if (ok) umma_commit_pair_pred(bar_tfull(acc), leader);
-#ifdef RL_TRACE
-        if (RL_DEBUG(512) && it == 0) {  // experiment: when does the issuing warp itself see the accumulator complete?
-          const uint32_t aph0 = 0u;
-          while (!mbar_try_wait(bar_tfull(acc), aph0)) {}
-          if (lane == 0) RL_GSTAMP(6);
-        }
-#endif
       }
     }
     __syncwarp();
