@@ -100,9 +100,9 @@ struct PairCfg {
 
 // One work item of a CTA pair: a whole tile (slice < 0, k-blocks [0, KB)), or one k-slice of a tail tile.
 //
-// Tiles are dealt round-robin, tile t to pair t % n_pairs.  A k-block of a 256 x 256 tile costs the tensor
-// pipe the same ~650 cycles whatever the tile's width (the MMA instruction has a fixed cost), so the only way
-// to spread the tiles of a partly filled last round over the idle pairs is along K: with tail_split = S each
+// Tiles are dealt round-robin, tile t to pair t % n_pairs.  The main loop runs at the same ~650 cycles per
+// k-block whatever the tile's width (measured: 256 x 64 strips gained nothing), so the way to spread the tiles
+// of a partly filled last round over the idle pairs is along K: with tail_split = S each
 // of the last `tail_tiles` tiles is cut into S k-slices that S different pairs compute at the same time (pair
 // u takes slice u % S of tail tile u / S); the S partial accumulators meet in the epilogue.
 struct PairItem {
