@@ -163,6 +163,29 @@ def test_tail_tiles_split_along_k(M, N, K, has_gamma):
     assert orc.rel_max_err(run(xs, gs, Ws, 1e-6), orc.reference_fp32(xs, gs, Ws, 1e-6)) <= BF16_TOL
 
 
+def test_k_split_calls_on_two_streams_at_once():
+    """The contributors of a k-split tile wait for each other inside the kernel.  Two streams launching such
+    kernels at the same time (each with its own workspace) share the SMs; every call must still complete, with the
+    same bits and a clean status."""
+    for (M, N, K) in [(4096, 6144, 4096), (512, 1024, 4096)]:
+        assert _tail_plan(M, N, K)[1] >= 2
+        x, gm, W = orc.make_inputs(M, N, K, seed=21)
+        xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+        ref = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+        torch.cuda.synchronize()
+        streams = [torch.cuda.Stream(device=DEV), torch.cuda.Stream(device=DEV)]
+        for s in streams:
+            s.wait_stream(torch.cuda.current_stream())
+        outs = []
+        for _ in range(6):
+            for s in streams:
+                with torch.cuda.stream(s):
+                    outs.append(kb.rmsnorm_linear(xd, gd, Wd, 1e-6))
+        torch.cuda.synchronize()
+        kb.check_status()
+        assert all(torch.equal(o, ref) for o in outs)
+
+
 def test_tail_split_in_the_plain_gemm():
     M, N, K = 768, 1280, 4096
     assert _tail_plan(M, N, K)[1] >= 2
