@@ -72,6 +72,8 @@ def test_tail_split_plan(lib):
     assert _plan(lib, 16384, 7168, 8192) == (16, 4)        # one of eight shards of the MLP layer: 1792 = 24 x 74 + 16
     assert _plan(lib, 512, 1024, 4096) == (8, 4)           # fewer tiles than pairs
     assert _plan(lib, 8192, 8192, 8192) == (0, 0)          # 1024 = 13 x 74 + 62: more than half a round
+    assert _plan(lib, 1024, 16384, 2048) == (0, 0)         # 34 tail tiles could only be halved, and K is short
+    assert _plan(lib, 1024, 16384, 4096) == (34, 2)
     for pairs in (1, 7, 60, 64, 74, 80):
         for (M, N) in [(4096, 6144), (300, 520), (8192, 14336), (1000, 1032)]:
             tiles = ((M + 255) // 256) * ((N + 255) // 256)
