@@ -30,10 +30,15 @@
 namespace rl {
 
 // Optional timeline instrumentation (compile with -DRL_TRACE): clock64 stamps of the first
-// RL_TRACE_N k-blocks of CTA pair 0, laid out [rank][event][index]; RL_DEBUG switches turn
-// parts of the kernel off for experiments (results become wrong): 1 = no transform work; 64 = only the MMA
-// issue stamps and one stamp per tile, 64 + 16 = only the one per tile.  Keep switches out of inner loops: a
-// branch around each load of the transform alone slowed the whole kernel by a fifth.
+// RL_TRACE_N k-blocks of CTA pair 0, laid out [rank][event][index].  Events: 0 producer issue, 1 transform
+// multiplies done, 2 MMA issue, 3 transform sees the x tile, 4 transform arrives, 5 MMA warp gets the
+// accumulator (per tile), 6 epilogue sees the accumulator complete, 7 accumulator drained (per tile).  Behind
+// them, for CTA 0 only: (globaltimer ns, clock64) pairs at kernel entry, set-up done, first MMA issue, last
+// epilogue issued, stores done, exit.  The debug word selects stamps (64 = only the MMA issue stamps and one
+// per tile; 64 + 16 = only the one per tile) and has one switch that changes the work (1 = the transform
+// does nothing; results become wrong, every barrier still gets its arrivals).  Switches must leave the
+// barrier protocol intact and stay out of inner loops: a branch around each load of the transform alone
+// slowed the whole kernel by a fifth, and stamps in the MMA loop add ~130 cycles per k-block.
 #ifdef RL_TRACE
 #define RL_TRACE_N 256
 #define RL_STAMP(ev, idx)                                                               \
