@@ -43,12 +43,14 @@ class ColumnParallelRMSNormLinear:
 
     `local_fn(x, gamma, W_local, eps) -> y_local` is the single-device operator
     (the CUDA kernel by default; the tests pass a CPU stand-in to exercise the
-    sharding and gather arithmetic over gloo).
+    sharding and gather arithmetic over gloo).  With e4m3 weights the rank also
+    holds its slice of the per-output-channel scales (`w_scale_local`, fp32
+    [n1 - n0]) and `local_fn` is called with `w_scale=` as the operator takes it.
     """
 
     def __init__(self, W_local: torch.Tensor, gamma: Optional[torch.Tensor], eps: float, N_total: int,
                  group: Optional[dist.ProcessGroup] = None, local_fn: Optional[Callable] = None,
-                 multiple: int = 8):
+                 multiple: int = 8, w_scale_local: Optional[torch.Tensor] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -58,7 +60,11 @@ class ColumnParallelRMSNormLinear:
         if W_local.shape[0] != self.n1 - self.n0:
             raise ValueError(
                 f"rank {self.rank} expects {self.n1 - self.n0} rows of W, got {W_local.shape[0]}")
+        if w_scale_local is not None and w_scale_local.shape != (self.n1 - self.n0,):
+            raise ValueError(
+                f"rank {self.rank} expects {self.n1 - self.n0} weight scales, got {tuple(w_scale_local.shape)}")
         self.W_local = W_local
+        self.w_scale_local = w_scale_local
         self.gamma = gamma
         self.eps = eps
         if local_fn is None:
@@ -67,6 +73,8 @@ class ColumnParallelRMSNormLinear:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """y[:, n0:n1] for this rank.  No communication."""
+        if self.w_scale_local is not None:
+            return self.local_fn(x, self.gamma, self.W_local, self.eps, w_scale=self.w_scale_local)
         return self.local_fn(x, self.gamma, self.W_local, self.eps)
 
     def gather(self, y_local: torch.Tensor) -> torch.Tensor:

@@ -34,6 +34,17 @@ def main():
         if M > 64 and rank == 0:
             y_full = kb.rmsnorm_linear(x.to(dev), gm.to(dev), W.to(dev), 1e-6)
             ok = ok and orc.rel_max_err(y_full[:, op.n0:op.n1], y_local.float()) <= 2.0 ** -7
+    # e4m3 weights: each rank holds its rows of Wq and its slice of the per-channel scales
+    M, N, K = 256, 1024, 1024
+    x, gm, W = orc.make_inputs(M, N, K, seed=8)
+    Wq, wsc = orc.quantize_weight_e4m3(W)
+    op = ColumnParallelRMSNormLinear(shard_rows(Wq, world, rank).contiguous().to(dev), gm.to(dev), 1e-6, N,
+                                     w_scale_local=shard_rows(wsc, world, rank).contiguous().to(dev))
+    y = op.gather(op.forward(x.to(dev)))
+    torch.cuda.synchronize()
+    kb.check_status()
+    ref = orc.reference_fp32(x, gm, Wq, 1e-6, w_scale=wsc)
+    ok = ok and y.shape == (M, N) and orc.rel_max_err(y.cpu(), ref) <= 5e-2   # the FP8 tolerance at small K
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -72,6 +72,17 @@ def _rank_main(rank, world, port, N, q):
         ok_local = torch.allclose(y_local, full[:, n0:n1], rtol=1e-5, atol=1e-6)
         y = op.gather(y_local)
         ok_full = y.shape == full.shape and torch.allclose(y, full, rtol=1e-5, atol=1e-6)
+        # e4m3 weights: the rank's slice of the per-channel scales travels with its rows of W
+        Wq, wsc = orc.quantize_weight_e4m3(W)
+
+        def cpu_stand_in_fp8(x_, g_, Wq_, eps, w_scale):
+            return orc.torch_rmsnorm_linear(x_, g_, Wq_.float() * w_scale[:, None], eps)
+
+        op8 = ColumnParallelRMSNormLinear(shard_rows(Wq, world, rank), gm, 1e-6, N, local_fn=cpu_stand_in_fp8,
+                                          w_scale_local=shard_rows(wsc, world, rank))
+        full8 = orc.torch_rmsnorm_linear(x, gm, Wq.float() * wsc[:, None], 1e-6)
+        y8 = op8.gather(op8.forward(x))
+        ok_full = ok_full and torch.allclose(y8, full8, rtol=1e-5, atol=1e-6)
         q.put((rank, bool(ok_local), bool(ok_full)))
     finally:
         dist.destroy_process_group()
@@ -96,6 +107,9 @@ def test_wrong_shard_size_is_rejected():
     W = torch.zeros(10, 16)
     with pytest.raises(ValueError, match="rows of W"):
         ColumnParallelRMSNormLinear(W, None, 1e-6, 64, local_fn=lambda *a: None)
+    with pytest.raises(ValueError, match="weight scales"):
+        ColumnParallelRMSNormLinear(torch.zeros(64, 16), None, 1e-6, 64, local_fn=lambda *a: None,
+                                    w_scale_local=torch.zeros(10))
 
 
 def test_harness_csv_contract(tmp_path):
