@@ -70,7 +70,7 @@ const char* rl_error_string(int code);
 size_t rl_workspace_bytes(int M, int N, int K, int w_dtype);
 
 /* How the M > 128 pre-pass kernels treat the last, partly filled round of 256 x 256 tiles on `pairs` CTA pairs
- * (74 on a B200): *tail_tiles tiles are each cut along K into *split (2 or 4) slices computed by different pairs
+ * (74 on a B200): *tail_tiles tiles are each cut along K into *split (2, 3 or 4) slices computed by different pairs
  * and summed in slice order; 0 / 0 = every tile computed whole.  Pure arithmetic, needs no GPU.  No reference
  * counterpart (its kernels leave scheduling to their DSL compilers). */
 int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* split);

@@ -227,6 +227,7 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
   // the exchange costs about as much as 15 k-blocks of the main loop (measured: ~5 us); split only when each pair
   // is spared clearly more than that: KB (1 - 1/S) >= 20
   if ((long long)r * 4 <= max_pairs && r * 4 * 2 <= RL_MAX_CTAS && KB >= 32) return TailPlan{r, 4};
+  if ((long long)r * 3 <= max_pairs && r * 3 * 2 <= RL_MAX_CTAS && KB >= 32) return TailPlan{r, 3};
   if ((long long)r * 2 <= max_pairs && r * 2 * 2 <= RL_MAX_CTAS && KB >= 40) return TailPlan{r, 2};
   return TailPlan{0, 0};
 }

@@ -30,7 +30,7 @@ struct PrefillParams {
   long long* trace;  // timeline stamps of CTA pair 0 (only read by builds with RL_TRACE)
   int debug;         // experiment switches, honoured only by builds with RL_TRACE (results become wrong)
   const float* row_rstd;  // [M] 1/rms per token from rowstats_kernel (kernels built with PRESTATS), else nullptr
-  // Pair kernels: the last `tail_tiles` tiles are each cut along K into `tail_split` (2 or 4) slices computed by
+  // Pair kernels: the last `tail_tiles` tiles are each cut along K into `tail_split` (2, 3 or 4) slices computed by
   // different CTA pairs (0 = off).  tail_counters: 2 per (tail tile, CTA rank), zero between launches;
   // tail_partials: one 128-row x 256-column fp32 block per (tail tile, slice, CTA rank).
   int tail_tiles, tail_split;

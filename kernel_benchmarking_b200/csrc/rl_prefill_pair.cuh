@@ -468,14 +468,15 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           // than the device holds), pulls the S - 1 other partials of its own columns through the idle operand
           // ring and adds them to its own in slice order, so the result does not depend on who came first.
           tail_done = true;
-          const int S = p.tail_split;                     // 2 or 4
-          const int nch = (BN / 64) / S;                  // 64-column chunks this CTA finishes
-          const int c_lo = w.slice * nch;
+          const int S = p.tail_split;                     // 2, 3 or 4
+          // the tile's four 64-column chunks are dealt to the S contributors as evenly as they go (S = 3: 1, 1, 2)
+          const int c_lo = (w.slice * (BN / 64)) / S;
+          const int nch = ((w.slice + 1) * (BN / 64)) / S - c_lo;
           const int tl = w.t - (total_tiles - p.tail_tiles);
           unsigned* cnt = p.tail_counters + 2 * (tl * 2 + (int)rank);  // [0] partials written, [1] waits passed
           constexpr int SLOT_F4 = 128 * BN / 4;                        // float4 per (tile, slice, rank) block
           constexpr uint32_t PART_BYTES = 64 * 128 * 4;                // 64 columns of a block: contiguous
-          static_assert(3 * PART_BYTES <= (uint32_t)Cfg::OFF_EPI, "partial buffers fit in the operand ring");
+          static_assert(4 * PART_BYTES <= (uint32_t)Cfg::OFF_EPI, "partial buffers ((S - 1) x chunks <= 4) fit in the operand ring");
           // block layout [column / 4][row] float4: a warp's 32 rows of one column group are 512 contiguous bytes
           float4* slot0 = reinterpret_cast<float4*>(p.tail_partials) + (size_t)(tl * S * 2 + (int)rank) * SLOT_F4;
           float4* mine = slot0 + (size_t)w.slice * 2 * SLOT_F4;

@@ -62,13 +62,14 @@ def _plan(lib, M, N, K, pairs=74):
 
 def test_tail_split_plan(lib):
     """Which tiles of the M > 128 kernels are cut along K: those of a last round that fills at most half the CTA
-    pairs, in 4 when a quarter of the pairs is enough, else in 2, and only when K is long enough to pay for the
-    exchange of partial sums."""
+    pairs, in as many slices (4, 3 or 2) as there are idle pairs for, and only when K is long enough to pay for
+    the exchange of partial sums."""
     assert _plan(lib, 16384, 28672, 8192) == (0, 0)        # 7168 tiles = 96.9 rounds: last round nearly full
     assert _plan(lib, 256 * 74, 256, 4096) == (0, 0)       # exactly one round
     assert _plan(lib, 512, 512, 1024) == (0, 0)            # K too short
     assert _plan(lib, 4096, 6144, 4096) == (14, 4)         # the prefill benchmark shape: 384 tiles = 5 rounds + 14
     assert _plan(lib, 4096, 4096, 4096) == (34, 2)         # 256 tiles = 3 rounds + 34
+    assert _plan(lib, 4096, 1536, 7168) == (22, 3)         # 96 tiles = 1 round + 22
     assert _plan(lib, 16384, 7168, 8192) == (16, 4)        # one of eight shards of the MLP layer: 1792 = 24 x 74 + 16
     assert _plan(lib, 512, 1024, 4096) == (8, 4)           # fewer tiles than pairs
     assert _plan(lib, 8192, 8192, 8192) == (0, 0)          # 1024 = 13 x 74 + 62: more than half a round
@@ -78,7 +79,7 @@ def test_tail_split_plan(lib):
         for (M, N) in [(4096, 6144), (300, 520), (8192, 14336), (1000, 1032)]:
             tiles = ((M + 255) // 256) * ((N + 255) // 256)
             tail, split = _plan(lib, M, N, 4096, pairs)
-            assert (tail, split) == (0, 0) or (tail == tiles % pairs and split in (2, 4) and tail * split <= pairs
+            assert (tail, split) == (0, 0) or (tail == tiles % pairs and split in (2, 3, 4) and tail * split <= pairs
                                                and 2 * tail * split <= 160)
     assert lib.rl_plan_tail_split(0, 1, 1, 74, None, None) != 0
 
