@@ -55,7 +55,7 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "prefill_qkv_4096x6144x4096"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries (profiles/)
 NCU_TRAFFIC_BYTES = {
-    "prefill_qkv_4096x6144x4096": 164.7e6,     # profiles/prefill_pair_kernel_4096x6144x4096_bf16.md
+    "prefill_qkv_4096x6144x4096": 164.4e6,     # profiles/prefill_pair_kernel_4096x6144x4096_bf16.md
     "decode_16x28672x4096": 240.3e6,           # profiles/decode_kernel_16x28672x4096_bf16.md
     "fp8w_8192x14336x4096": 465.0e6,           # profiles/fp8_pair_kernel_8192x14336x4096_e4m3.md (GEMM kernel only)
 }
