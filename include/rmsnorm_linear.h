@@ -3,9 +3,23 @@
  *     y[m, n] = rsqrt(mean_k x[m,k]^2 + eps) * sum_k x[m,k] * gamma[k] * W[n,k]
  *
  * Every entry point takes plain pointers and sizes; device pointers belong to
- * the caller, the library never allocates, frees or keeps device memory, and
- * every launch is asynchronous on the stream that is passed in.  All functions
- * return 0 on success or a negative RL_ERR_* code; nothing throws.
+ * the caller, and every launch is asynchronous on the stream that is passed in.
+ * The library never calls an allocator and keeps no pointer of the caller's; the
+ * one piece of device memory it owns is the fixed 3 MiB scratch array of
+ * rl_rmsnorm_linear_bf16_noalloc, which is part of the library's device image
+ * (see that function).  All functions return 0 on success or a negative RL_ERR_*
+ * code; nothing throws.
+ *
+ * Concurrency.  Calls on one stream may follow each other freely.  The large-M
+ * kernels that cut the tiles of a partly filled last round along K
+ * (rl_plan_tail_split) make CTA pairs of one launch wait for each other through
+ * the workspace, which relies on the whole grid being resident: keep at most
+ * one such launch in flight per device, or pass RL_VARIANT_AUTO_WHOLE on the
+ * streams that run concurrently - the same choice of kernels with every tile
+ * computed whole and no CTA waiting for another.  Two such launches sharing
+ * the SMs can starve each other; each then gives up after its wait limit (2 s)
+ * with RL_ERR_DEVICE_TIMEOUT in the status block, its output is wrong, and the
+ * workspace must be cleared with rl_workspace_init before it is used again.
  *
  * Each function names the interface of the reference project
  * (dungwoong/kernel-benchmarking) that it stands in for.
@@ -53,7 +67,9 @@ enum {
   RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE = 15, /* as 14, every tile computed whole by one pair */
   RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS = 16, /* gamma == NULL only: 1/rms from the pre-pass, x straight from shared memory, two accumulators */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
-  RL_VARIANT_DECODE = 20           /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
+  RL_VARIANT_DECODE = 20,          /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
+  RL_VARIANT_AUTO_WHOLE = 30       /* as AUTO, but never a kernel whose CTAs wait for one another (no k-split last round):
+                                      for callers that keep several launches in flight on one device */
 };
 
 /* Library version (major * 1000 + minor).  No reference counterpart. */
@@ -74,6 +90,12 @@ size_t rl_workspace_bytes(int M, int N, int K, int w_dtype);
  * and summed in slice order; 0 / 0 = every tile computed whole.  Pure arithmetic, needs no GPU.  No reference
  * counterpart (its kernels leave scheduling to their DSL compilers). */
 int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* split);
+
+/* The variant RL_VARIANT_AUTO runs for a bf16 call of this shape on the current device (it asks the device for its
+ * SM count and CTA-pair occupancy, so it needs a GPU); a negative RL_ERR_* code on failure.  Lets a benchmark label
+ * its numbers with the kernel that ran.  No reference counterpart (the reference's kernels are picked by name in
+ * its `kernels` dict, demo/new_profiling/rmsnorm_linear_new.py:97-103). */
+int rl_select_variant(int M, int N, int K, int has_gamma, int has_workspace);
 
 /* Zero the workspace (status block and tile counters) on `stream`.  Must run
  * once before the first use of a workspace; kernels leave it clean afterwards. */
@@ -101,7 +123,8 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
  *   The normalised activations are quantised to e4m3 per token on the device:
  *   q = e4m3(x * gamma * 448 / amax_m); y = (q @ Wq^T) * rsqrt(mean x^2 + eps) * amax_m / 448 * w_scale[n].
  *   K and ldw must be multiples of 16.  The workspace (rl_workspace_bytes with RL_W_E4M3) holds
- *   the quantised activations and the per-token scales.
+ *   the quantised activations, the per-token scales and the partial blocks of a k-split last round.
+ *   `variant`: RL_VARIANT_AUTO or RL_VARIANT_AUTO_WHOLE.
  * No reference counterpart: the reference project has no quantised path; the operator semantics
  * are those of rl_rmsnorm_linear_bf16 applied to the dequantised weights. */
 int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, const float* w_scale, void* y,
@@ -134,6 +157,9 @@ int rl_quantize_rows_e4m3(const void* x, const void* gamma, void* q, float* row_
  *
  *   - Limit: M <= 16 tokens (any N and K the small-M kernel accepts); larger M returns
  *     RL_ERR_STATIC_SCRATCH.  The 3 MiB stay resident on every GPU that loads the library until exit.
+ *     They are claimed when the CUDA runtime loads the library's device image on that GPU, which with
+ *     lazy loading can be inside the first call: on a device with no memory left that call returns
+ *     RL_ERR_CUDA - cudaErrorMemoryAllocation.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
  *     should therefore be made, once per device, before any stream capture begins.
  *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different

@@ -10,7 +10,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 # RMSNORM_LINEAR_LIB points the loader at another build of the library (e.g. an instrumented one)
 LIB_PATH = os.environ.get("RMSNORM_LINEAR_LIB") or os.path.join(PKG_DIR, "librmsnorm_linear.so")
 SOURCES = ["rl_api.cu"]
-HEADERS = ["rl_ptx.cuh", "rl_prefill.cuh", "rl_prefill_pair.cuh", "rl_decode.cuh", "rl_fp8_pair.cuh"]
+HEADERS = ["rl_ptx.cuh", "rl_prefill.cuh", "rl_prefill_pair.cuh", "rl_decode.cuh", "rl_rowquant.cuh"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC", "-cudart", "static",

@@ -40,7 +40,9 @@ VARIANTS = {
     "prefill_pair_prestats_whole": 15,
     "prefill_pair_direct_prestats": 16,
     "decode": 20,
+    "auto_whole": 30,
 }
+VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 
 # every symbol include/rmsnorm_linear.h declares: (name, restype, argtypes)
 _vp, _i, _i64, _sz, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t, ctypes.c_float
@@ -49,6 +51,7 @@ SYMBOLS = [
     ("rl_error_string", ctypes.c_char_p, [_i]),
     ("rl_workspace_bytes", _sz, [_i, _i, _i, _i]),
     ("rl_plan_tail_split", _i, [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
+    ("rl_select_variant", _i, [_i, _i, _i, _i, _i]),
     ("rl_workspace_init", _i, [_vp, _sz, _vp]),
     ("rl_rmsnorm_linear_bf16", _i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),
     ("rl_rmsnorm_linear_fp8w", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _f, _vp, _sz, _i, _vp]),

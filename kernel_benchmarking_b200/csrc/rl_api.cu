@@ -3,11 +3,10 @@
 #include "../../include/rmsnorm_linear.h"
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "rl_decode.cuh"
-#include "rl_fp8_pair.cuh"
+#include "rl_rowquant.cuh"
 #include "rl_prefill.cuh"
 #include "rl_prefill_pair.cuh"
 
@@ -162,6 +161,16 @@ WsLayout ws_layout(int M, int N) {
   return w;
 }
 
+// The CTA-pair configurations the entry points use: <BN, accumulators, ring stages, A slots in tensor memory,
+// transform groups, A operand mode, 1/rms from the pre-pass, SwiGLU epilogue, FP8 operands>.
+using PairFold = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true>;        // gamma folded through tensor memory; k-split tail
+using PairFoldFused = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD>;         // the same with the sums of squares in the transform
+using PairFoldN192 = PairCfg<192, 2, 6, 4, 2, A_TS_FOLD>;
+using PairDirectFused = PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT>;     // no gamma: x straight from shared memory
+using PairDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true>;    // ... with 1/rms from the pre-pass (or no norm at all)
+using PairSwiglu = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>;
+using PairFp8 = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, false, true>;
+
 template <class Cfg>
 int launch_prefill(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                    int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st) {
@@ -232,70 +241,112 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
   return TailPlan{0, 0};
 }
 
+// Row tiles (of 256 tokens) per sweep group.  Tiles are walked group by group, a group's row tiles against every
+// column tile, so the x rows of one group stay in L2 while W streams past; W is read from DRAM once per group.
+// The group is made as large as fits a budget well inside the 126 MB L2 (x of the group, the W tiles in flight
+// and the y tiles on their way out share it): when all of x fits, W streams exactly once.
+#ifndef RL_GROUP_BUDGET_MB
+#define RL_GROUP_BUDGET_MB 40
+#endif
+int pick_group_m(int m_tiles, long long row_tile_bytes) {
+  long long g = ((long long)RL_GROUP_BUDGET_MB << 20) / (row_tile_bytes > 0 ? row_tile_bytes : 1);
+  if (g < 4) g = 4;
+  if (g > m_tiles) g = m_tiles;
+  const long long groups = (m_tiles + g - 1) / g;  // even the groups out
+  return (int)((m_tiles + groups - 1) / groups);
+}
+
+// Everything a launch of the CTA-pair kernel needs besides its configuration.
+struct PairArgs {
+  const void* x = nullptr;             // [M, K] bf16 (FP8: e4m3 activations from rowquant_kernel)
+  const __nv_bfloat16* gamma = nullptr;
+  const void* W = nullptr;             // [N, K] (SwiGLU: [2N, K])
+  void* y = nullptr;
+  int M = 0, N = 0, K = 0;
+  int64_t ldx = 0, ldw = 0, ldy = 0;
+  float eps = 0.f;
+  int* status = nullptr;               // start of the workspace, or nullptr
+  size_t ws_bytes = 0;
+  size_t tail_off = 0, ws_total = 0;   // where the partial blocks of k-split tiles live, and the size that holds them
+  int sms = 0;
+  cudaStream_t st = nullptr;
+  bool no_norm = false;                // plain GEMM: no row statistics at all
+  bool split_tail = true;
+  const void* x2 = nullptr;            // LoRA: second operand pair [M, L] / [N, L]
+  const void* w2 = nullptr;
+  int L = 0;
+  int64_t ldx2 = 0, ldw2 = 0;
+  const float* row_scale = nullptr;    // FP8: per-token scale (already computed on `st`)
+  const float* w_scale = nullptr;      // FP8: per-channel weight scales
+};
+
 template <class Cfg>
-int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
-                        int64_t ldx, int64_t ldw, int64_t ldy, float eps, int* status, int sms, cudaStream_t st,
-                        bool no_norm = false, size_t ws_bytes = 0, bool split_tail = true, const void* x2 = nullptr,
-                        const void* w2 = nullptr, int L = 0, int64_t ldx2 = 0, int64_t ldw2 = 0) {
+int launch_prefill_pair(const PairArgs& a) {
   CUtensorMap tx, tw, ty, tx2, tw2;
   int rc;
-  if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, 128))) return rc;
-  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, ldw, 64,
-                     Cfg::BN / 2)))
+  const int M = a.M, N = a.N, K = a.K;
+  const CUtensorMapDataType dt = Cfg::FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int eb = Cfg::FP8 ? 1 : 2;
+  if ((rc = make_map(&tx, dt, eb, a.x, K, M, a.ldx, Cfg::KBW, 128))) return rc;
+  if ((rc = make_map(&tw, dt, eb, a.W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, a.ldw, Cfg::KBW, Cfg::BN / 2)))
     return rc;
-  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
-  if (Cfg::AMODE == A_SS_DIRECT && gamma != nullptr) return RL_ERR_BAD_VARIANT;
+  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, N, M, a.ldy, 64, 128))) return rc;
+  if (Cfg::AMODE == A_SS_DIRECT && a.gamma != nullptr) return RL_ERR_BAD_VARIANT;
   tx2 = tx;
   tw2 = tw;
-  if (x2 != nullptr) {
+  if (a.x2 != nullptr) {
     // second operand pair [M, L] / [N, L]: same boxes as the first, columns L..63 come back as zeros
-    if (Cfg::AMODE != A_SS_DIRECT || Cfg::SWIGLU || L <= 0 || L > 64) return RL_ERR_BAD_VARIANT;
-    if ((rc = make_map(&tx2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x2, L, M, ldx2, 64, 128))) return rc;
-    if ((rc = make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w2, L, (uint64_t)N, ldw2, 64, Cfg::BN / 2))) return rc;
+    if (Cfg::AMODE != A_SS_DIRECT || Cfg::SWIGLU || Cfg::FP8 || a.L <= 0 || a.L > 64) return RL_ERR_BAD_VARIANT;
+    if ((rc = make_map(&tx2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x2, a.L, M, a.ldx2, 64, 128))) return rc;
+    if ((rc = make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.w2, a.L, (uint64_t)N, a.ldw2, 64, Cfg::BN / 2))) return rc;
   }
   PrefillParams p{};
-  p.M = M; p.N = N; p.K = K; p.eps = eps;
-  p.gamma = gamma;
+  p.M = M; p.N = N; p.K = K; p.eps = a.eps;
+  p.gamma = a.gamma;
   p.m_tiles = (M + 255) / 256;
   p.n_tiles = Cfg::SWIGLU ? (N + 127) / 128 : (N + Cfg::BN - 1) / Cfg::BN;  // SwiGLU: N = output channels, W has 2N rows
-  p.group_m = 8;
-  p.status = status;
-  p.extra_kb = (x2 != nullptr) ? 1 : 0;
-  if (Cfg::PRESTATS && !no_norm) {
-    if (status == nullptr) return RL_ERR_WORKSPACE;
-    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + ws_layout(M > 65 ? M : 65, N).rstd_off);
-    rowstats_kernel<<<(M + 3) / 4, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), rstd, M, K, ldx, eps);
+  p.group_m = pick_group_m(p.m_tiles, (long long)256 * K * eb);
+  p.status = a.status;
+  p.extra_kb = (a.x2 != nullptr) ? 1 : 0;
+  p.w_scale = a.w_scale;
+  if (Cfg::FP8) {
+    if (a.row_scale == nullptr || a.w_scale == nullptr) return RL_ERR_NULL_POINTER;
+    p.row_rstd = a.row_scale;
+  } else if (Cfg::PRESTATS && !a.no_norm) {
+    if (a.status == nullptr) return RL_ERR_WORKSPACE;
+    float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.status) + ws_layout(M > 65 ? M : 65, N).rstd_off);
+    rowstats_kernel<<<(M + 3) / 4, 128, 0, a.st>>>(reinterpret_cast<const __nv_bfloat16*>(a.x), rstd, M, K, a.ldx, a.eps);
     p.row_rstd = rstd;
   }
-#ifdef RL_TRACE
-  p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
-  p.trace = status ? reinterpret_cast<long long*>(reinterpret_cast<uint8_t*>(status) + 4096) : nullptr;
-#endif
   cudaError_t e = set_smem_once(prefill_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   int max_pairs = 0;
-  if ((rc = max_cta_pairs<Cfg>(sms, &max_pairs))) return rc;
+  if ((rc = max_cta_pairs<Cfg>(a.sms, &max_pairs))) return rc;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && split_tail && status != nullptr) {
-    const WsLayout wl = ws_layout(M > 65 ? M : 65, N);
-    const TailPlan tp = plan_tail(tiles, max_pairs, (K + 63) / 64 + p.extra_kb);
-    if (tp.split > 1 && ws_bytes >= wl.total) {
+  if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && a.split_tail && a.status != nullptr) {
+    const TailPlan tp = plan_tail(tiles, max_pairs, (K + Cfg::KBW - 1) / Cfg::KBW + p.extra_kb);
+    if (tp.split > 1 && a.ws_total > 0 && a.ws_bytes >= a.ws_total) {
       p.tail_tiles = tp.tiles;
       p.tail_split = tp.split;
-      p.tail_counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(status) + wl.counters_off);
-      p.tail_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(status) + wl.tail_off);
+      p.tail_counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(a.status) + STATUS_BYTES);
+      p.tail_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.status) + a.tail_off);
       if (tiles < max_pairs) pairs = tp.tiles * tp.split;  // fewer tiles than pairs: every tile is cut
     }
   }
-  if (Cfg::PRESTATS) {
-    // behind rowstats_kernel with programmatic stream serialisation: the GEMM streams its tiles while the
-    // row statistics are still being computed and waits only where it first reads them
+  if (Cfg::PRESTATS && p.row_rstd != nullptr) {
+    // behind rowstats_kernel (FP8: rowquant_kernel) with programmatic stream serialisation: the GEMM sets up
+    // and, in the bf16 case, streams its tiles while the row statistics are still being computed, and waits only
+    // where it first reads them.  Only in that case: the kernel in front is a normal launch, so everything
+    // earlier in the stream (whoever wrote x and W) is complete before it starts, and the producer warp may load
+    // the caller's operands without waiting.  With the norm switched off nothing is launched in front, and the
+    // kernel must not become a programmatic dependent of whatever the caller ran before it: it is launched
+    // normally below.
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(2 * pairs));
     lc.blockDim = dim3(Cfg::THREADS);
     lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    lc.stream = st;
+    lc.stream = a.st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
@@ -304,7 +355,7 @@ int launch_prefill_pair(const void* x, const __nv_bfloat16* gamma, const void* W
     e = cudaLaunchKernelEx(&lc, prefill_pair_kernel<Cfg>, tx, tw, ty, tx2, tw2, p);
     return e == cudaSuccess ? RL_OK : cuda_err(e);
   }
-  prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tx, tw, ty, tx2, tw2, p);
+  prefill_pair_kernel<Cfg><<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, a.st>>>(tx, tw, ty, tx2, tw2, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
@@ -332,9 +383,6 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   p.counters = reinterpret_cast<int*>(ws + wl.counters_off);
   p.ssq_partials = reinterpret_cast<float*>(ws + wl.ssq_off);
   p.partials = reinterpret_cast<float*>(ws + wl.partials_off);
-#ifdef RL_TRACE
-  p.debug = getenv("RL_DEBUG") ? atoi(getenv("RL_DEBUG")) : 0;
-#endif
   int grid = sms < RL_MAX_CTAS ? sms : RL_MAX_CTAS;
   if (units < grid) grid = (int)units;
   cudaError_t e = set_smem_once(decode_kernel<Cfg>, Cfg::SMEM_BYTES);
@@ -357,13 +405,15 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
 }
 
 struct Fp8WsLayout {
-  size_t row_scale_off, xq_off, total;
+  size_t row_scale_off, xq_off, tail_off, min_total, total;
 };
 Fp8WsLayout fp8_ws_layout(int M, int K) {
   Fp8WsLayout w{};
   w.row_scale_off = STATUS_BYTES + COUNTER_BYTES;  // behind the tile-counter region, which must stay zero
   w.xq_off = align_up(w.row_scale_off + (size_t)M * 4, 1024);
-  w.total = w.xq_off + (size_t)M * (size_t)K;
+  w.tail_off = align_up(w.xq_off + (size_t)M * (size_t)K, 1024);
+  w.min_total = w.tail_off;            // enough to run; the tail tiles are then computed whole
+  w.total = w.tail_off + TAIL_BYTES;   // with room for the partial blocks of k-split tail tiles
   return w;
 }
 
@@ -377,41 +427,6 @@ int launch_rowquant(const void* x, const void* gamma, void* q, float* row_scale,
   p.M = M; p.K = K; p.ldx = ldx; p.ldq = ldq; p.eps = eps;
   rowquant_kernel<<<M, 128, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? RL_OK : cuda_err(e);
-}
-
-template <class Cfg>
-int launch_fp8_pair(const void* xq, const float* row_scale, const void* Wq, const float* w_scale, void* y, int M, int N,
-                    int K, int64_t ldq, int64_t ldw, int64_t ldy, int* status, int sms, cudaStream_t st) {
-  CUtensorMap ta, tw, ty;
-  int rc;
-  if ((rc = make_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, K, M, ldq, 128, 128))) return rc;
-  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, K, N, ldw, 128, 128))) return rc;
-  if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, N, M, ldy, 64, 128))) return rc;
-  Fp8GemmParams p{};
-  p.M = M; p.N = N; p.K = K;
-  p.row_scale = row_scale;
-  p.w_scale = w_scale;
-  p.m_tiles = (M + 255) / 256;
-  p.n_tiles = (N + 255) / 256;
-  p.group_m = 8;
-  p.status = status;
-  cudaError_t e = set_smem_once(fp8_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
-  if (e != cudaSuccess) return cuda_err(e);
-  const long long tiles = (long long)p.m_tiles * p.n_tiles;
-  const int max_pairs = sms / 2;
-  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3((unsigned)(2 * pairs));
-  lc.blockDim = dim3(Cfg::THREADS);
-  lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  lc.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // prologue overlaps the quantisation kernel's tail
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  lc.attrs = at;
-  lc.numAttrs = 1;
-  e = cudaLaunchKernelEx(&lc, fp8_pair_kernel<Cfg>, ta, tw, ty, p);
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
@@ -460,6 +475,25 @@ int static_scratch_address(uint8_t** out) {
   return RL_OK;
 }
 
+// What RL_VARIANT_AUTO runs for a bf16 call.
+int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms) {
+  if (M <= 64) return RL_VARIANT_DECODE;
+  if (M <= 128) return RL_VARIANT_PREFILL_TS_N192;
+  // Without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
+  // which frees tensor memory for a second accumulator.
+  // Row statistics: from the overlapped pre-pass when there is a workspace and more than one round of tiles
+  // (or few enough tiles that their k-loops get split): every column tile would otherwise recompute the same
+  // sums on warps that share schedulers with the MMA warp.  With one round, not split, the pre-pass only adds
+  // a second read of x and a launch in front of an epilogue that has to wait for it (12-15 % at K >= 4096):
+  // there the transform warps accumulate the sums themselves.
+  int pairs = sms / 2;
+  (void)max_cta_pairs<PairFold>(sms, &pairs);
+  const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  const bool one_round = tiles <= pairs && 2 * tiles > pairs;
+  if (!has_workspace || one_round) return has_gamma ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_PAIR_DIRECT;
+  return has_gamma ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -502,6 +536,15 @@ int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* spl
   return RL_OK;
 }
 
+int rl_select_variant(int M, int N, int K, int has_gamma, int has_workspace) {
+  if (M <= 0 || N <= 0 || K <= 0) return RL_ERR_BAD_SHAPE;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
+  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms);
+}
+
 int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace) return RL_ERR_NULL_POINTER;
   if (workspace_bytes < STATUS_BYTES) return RL_ERR_WORKSPACE;
@@ -516,6 +559,8 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   if (M <= 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N) return RL_ERR_BAD_SHAPE;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || !aligned16(x) || !aligned16(W) || (gamma && !aligned16(gamma)))
     return RL_ERR_ALIGNMENT;
+  const bool auto_whole = (variant == RL_VARIANT_AUTO_WHOLE);  // AUTO, but no kernel whose CTAs wait for each other
+  if (auto_whole) variant = RL_VARIANT_AUTO;
   const bool decode = (variant == RL_VARIANT_DECODE) || (variant == RL_VARIANT_AUTO && M <= 64);
   if (decode && M > 64) return RL_ERR_BAD_VARIANT;
   if (!decode && ((ldy & 7) || !aligned16(y))) return RL_ERR_ALIGNMENT;
@@ -538,26 +583,13 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   }
 
   // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
-  if (variant == RL_VARIANT_AUTO) {
-    if (M <= 128) {
-      variant = RL_VARIANT_PREFILL_TS_N192;
-    } else {
-      // Without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
-      // which frees tensor memory for a second accumulator.
-      // Row statistics: from the overlapped pre-pass when there is a workspace and more than one round of tiles
-      // (or few enough tiles that their k-loops get split): every column tile would otherwise recompute the same
-      // sums on warps that share schedulers with the MMA warp.  With one round, not split, the pre-pass only adds
-      // a second read of x and a launch in front of an epilogue that has to wait for it (12-15 % at K >= 4096):
-      // there the transform warps accumulate the sums themselves.
-      int pairs = di.sms / 2;
-      (void)max_cta_pairs<PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true>>(di.sms, &pairs);
-      const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-      const bool one_round = tiles <= pairs && 2 * tiles > pairs;
-      if (!workspace || one_round) variant = g ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_PAIR_DIRECT;
-      else variant = g ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
-    }
-  }
-  const bool split_tail = (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
+  if (variant == RL_VARIANT_AUTO) variant = select_variant(M, N, g != nullptr, workspace != nullptr, di.sms);
+  const bool split_tail = !auto_whole && (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
+  PairArgs pa;
+  pa.x = x; pa.gamma = g; pa.W = W; pa.y = y;
+  pa.M = M; pa.N = N; pa.K = K; pa.ldx = ldx; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;
+  pa.status = status; pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
+  pa.sms = di.sms; pa.st = st; pa.split_tail = split_tail;
 #define RL_PREFILL(BN, ST, AM, TG) \
   launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
   switch (variant) {
@@ -566,16 +598,12 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_SS_N256: return g ? RL_PREFILL(256, 4, A_SS_FOLD, 1) : RL_PREFILL(256, 4, A_SS_DIRECT, 1);
     case RL_VARIANT_PREFILL_TS_N128: return RL_PREFILL(128, 4, A_TS_FOLD, 2);
     case RL_VARIANT_PREFILL_SS_N128: return g ? RL_PREFILL(128, 4, A_SS_FOLD, 2) : RL_PREFILL(128, 4, A_SS_DIRECT, 2);
-#define RL_PAIR(BN, NACC, ST, AS, TG, AM, ...) \
-  launch_prefill_pair<PairCfg<BN, NACC, ST, AS, TG, AM, ##__VA_ARGS__>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, \
-                                                                       di.sms, st, false, workspace_bytes, split_tail)
-    case RL_VARIANT_PREFILL_PAIR_N256: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD);
-    case RL_VARIANT_PREFILL_PAIR_N192: return RL_PAIR(192, 2, 6, 4, 2, A_TS_FOLD);
-    case RL_VARIANT_PREFILL_PAIR_DIRECT: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT);
+    case RL_VARIANT_PREFILL_PAIR_N256: return launch_prefill_pair<PairFoldFused>(pa);
+    case RL_VARIANT_PREFILL_PAIR_N192: return launch_prefill_pair<PairFoldN192>(pa);
+    case RL_VARIANT_PREFILL_PAIR_DIRECT: return launch_prefill_pair<PairDirectFused>(pa);
     case RL_VARIANT_PREFILL_PAIR_PRESTATS:
-    case RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE: return RL_PAIR(256, 1, 6, 6, 2, A_TS_FOLD, true);
-    case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return RL_PAIR(256, 2, 6, 1, 2, A_SS_DIRECT, true);
-#undef RL_PAIR
+    case RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE: return launch_prefill_pair<PairFold>(pa);
+    case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return launch_prefill_pair<PairDirect>(pa);
     default: return RL_ERR_BAD_VARIANT;
   }
 #undef RL_PREFILL
@@ -610,9 +638,9 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
   if ((K & 15) || (ldx & 7) || (ldw & 15) || (ldy & 7) || !aligned16(x) || !aligned16(Wq) || !aligned16(y) ||
       (gamma && !aligned16(gamma)))
     return RL_ERR_ALIGNMENT;
-  if (variant != RL_VARIANT_AUTO) return RL_ERR_BAD_VARIANT;
+  if (variant != RL_VARIANT_AUTO && variant != RL_VARIANT_AUTO_WHOLE) return RL_ERR_BAD_VARIANT;
   const Fp8WsLayout wl = fp8_ws_layout(M, K);
-  if (!workspace || workspace_bytes < wl.total) return RL_ERR_WORKSPACE;
+  if (!workspace || workspace_bytes < wl.min_total) return RL_ERR_WORKSPACE;
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
@@ -622,8 +650,14 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
   float* row_scale = reinterpret_cast<float*>(ws + wl.row_scale_off);
   uint8_t* xq = ws + wl.xq_off;
   if ((rc = launch_rowquant(x, gamma, xq, row_scale, M, K, ldx, K, eps, st))) return rc;
-  return launch_fp8_pair<Fp8PairCfg<6>>(xq, row_scale, Wq, w_scale, y, M, N, K, K, ldw, ldy, reinterpret_cast<int*>(ws),
-                                        di.sms, st);
+  PairArgs pa;
+  pa.x = xq; pa.W = Wq; pa.y = y;
+  pa.M = M; pa.N = N; pa.K = K; pa.ldx = K; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;
+  pa.status = reinterpret_cast<int*>(ws); pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
+  pa.sms = di.sms; pa.st = st;
+  pa.split_tail = (variant != RL_VARIANT_AUTO_WHOLE);
+  pa.row_scale = row_scale; pa.w_scale = w_scale;
+  return launch_prefill_pair<PairFp8>(pa);
 }
 
 int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void* W, void* y, int M, int N, int K,
@@ -666,9 +700,12 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return launch_prefill_pair<PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>>(
-      x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw, ldy, eps,
-      reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream);
+  PairArgs pa;
+  pa.x = x; pa.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma); pa.W = W; pa.y = y;
+  pa.M = M; pa.N = N; pa.K = K; pa.ldx = ldx; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;
+  pa.status = reinterpret_cast<int*>(workspace); pa.ws_bytes = workspace_bytes;
+  pa.sms = di.sms; pa.st = (cudaStream_t)stream;
+  return launch_prefill_pair<PairSwiglu>(pa);
 }
 
 int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
@@ -682,9 +719,14 @@ int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
-      A, nullptr, B, C, M, N, K, lda, ldb, ldc, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
-      /*no_norm=*/true, workspace_bytes);
+  const WsLayout wl = ws_layout(M > 65 ? M : 65, N);
+  PairArgs pa;
+  pa.x = A; pa.W = B; pa.y = C;
+  pa.M = M; pa.N = N; pa.K = K; pa.ldx = lda; pa.ldw = ldb; pa.ldy = ldc;
+  pa.status = reinterpret_cast<int*>(workspace); pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
+  pa.sms = di.sms; pa.st = (cudaStream_t)stream;
+  pa.no_norm = true;
+  return launch_prefill_pair<PairDirect>(pa);
 }
 
 int rl_lora_linear_bf16(const void* a, const void* b, const void* xa, const void* lb, void* y, int M, int N, int K, int L,
@@ -701,9 +743,15 @@ int rl_lora_linear_bf16(const void* a, const void* b, const void* xa, const void
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return launch_prefill_pair<PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT, true>>(
-      a, nullptr, b, y, M, N, K, lda, ldb, ldy, 0.f, reinterpret_cast<int*>(workspace), di.sms, (cudaStream_t)stream,
-      /*no_norm=*/true, workspace_bytes, /*split_tail=*/true, xa, lb, L, ldxa, ldlb);
+  const WsLayout wl = ws_layout(M > 65 ? M : 65, N);
+  PairArgs pa;
+  pa.x = a; pa.W = b; pa.y = y;
+  pa.M = M; pa.N = N; pa.K = K; pa.ldx = lda; pa.ldw = ldb; pa.ldy = ldy;
+  pa.status = reinterpret_cast<int*>(workspace); pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
+  pa.sms = di.sms; pa.st = (cudaStream_t)stream;
+  pa.no_norm = true;
+  pa.x2 = xa; pa.w2 = lb; pa.L = L; pa.ldx2 = ldxa; pa.ldw2 = ldlb;
+  return launch_prefill_pair<PairDirect>(pa);
 }
 
 int rl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned long long limit_ns, void* stream) {

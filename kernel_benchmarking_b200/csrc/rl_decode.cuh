@@ -30,14 +30,7 @@ struct DecodeParams {
   int* counters;        // [n_tiles], zero between launches
   float* partials;      // [grid][2][MPAD][128]
   float* ssq_partials;  // [grid][2][MPAD]
-  int debug;            // experiment switches, honoured only by builds with RL_TRACE (results become wrong)
 };
-
-#ifdef RL_TRACE
-#define RL_DDEBUG(bit) ((p.debug & (bit)) != 0)
-#else
-#define RL_DDEBUG(bit) false
-#endif
 
 template <int MPAD_, int STAGES_>
 struct DecodeCfg {
@@ -219,9 +212,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
           const uint64_t adesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_W + s * Cfg::W_BYTES);
           const uint64_t bdesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_X + s * Cfg::X_BYTES);
           if (elect_one()) {
-            if (!RL_DDEBUG(1))
 #pragma unroll
-              for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+            for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
             umma_commit(bar_empty(s));
           }
           __syncwarp();
@@ -256,11 +248,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         ok = mbar_wait(bar_full(s), ph, ctl, 2, s, u + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (RL_DDEBUG(2)) {  // experiment: no tile work
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_xf(s));
-          continue;
-        }
         uint8_t* xt = smem + Cfg::OFF_X + s * Cfg::X_BYTES;
         const int kvalid = p.K - (kb0 + i) * 64;
         uint4 gv = make_uint4(0, 0, 0, 0);
@@ -331,12 +318,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       named_bar_sync(4, 128);
       if (*epi_go == 0) break;
       tc_fence_after();
-      if (RL_DDEBUG(4)) {  // experiment: no epilogue work
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty(acc));
-        continue;
-      }
 
       float a[MPAD];
 #pragma unroll

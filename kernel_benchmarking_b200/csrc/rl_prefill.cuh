@@ -27,9 +27,9 @@ struct PrefillParams {
   const __nv_bfloat16* gamma;  // [K] or nullptr (only with A_SS_DIRECT / treated as ones)
   int m_tiles, n_tiles, group_m;
   int* status;  // RL_STATUS_INTS ints or nullptr
-  long long* trace;  // timeline stamps of CTA pair 0 (only read by builds with RL_TRACE)
-  int debug;         // experiment switches, honoured only by builds with RL_TRACE (results become wrong)
-  const float* row_rstd;  // [M] 1/rms per token from rowstats_kernel (kernels built with PRESTATS), else nullptr
+  const float* row_rstd;  // [M] 1/rms per token from rowstats_kernel (kernels built with PRESTATS), else nullptr;
+                          // FP8 pair kernel: the per-token scale rsqrt(mean x^2 + eps) * amax / 448 from rowquant_kernel
+  const float* w_scale;   // FP8 pair kernel: [N] per-output-channel weight scales
   // Pair kernels: the last `tail_tiles` tiles are each cut along K into `tail_split` (2, 3 or 4) slices computed by
   // different CTA pairs (0 = off).  tail_counters: 2 per (tail tile, CTA rank), zero between launches;
   // tail_partials: one 128-row x 256-column fp32 block per (tail tile, slice, CTA rank).

@@ -29,44 +29,14 @@
 
 namespace rl {
 
-// Optional timeline instrumentation (compile with -DRL_TRACE): clock64 stamps of the first
-// RL_TRACE_N k-blocks of CTA pair 0, laid out [rank][event][index].  Events: 0 producer issue, 1 transform
-// multiplies done, 2 MMA issue, 3 transform sees the x tile, 4 transform arrives, 5 MMA warp gets the
-// accumulator (per tile), 6 epilogue sees the accumulator complete, 7 accumulator drained (per tile).  Behind
-// them, for CTA 0 only: (globaltimer ns, clock64) pairs at kernel entry, set-up done, first MMA issue, last
-// epilogue issued, stores done, exit.  The debug word selects stamps (64 = only the MMA issue stamps and one
-// per tile; 64 + 16 = only the one per tile) and has one switch that changes the work (1 = the transform
-// does nothing; results become wrong, every barrier still gets its arrivals).  Switches must leave the
-// barrier protocol intact and stay out of inner loops: a branch around each load of the transform alone
-// slowed the whole kernel by a fifth, and stamps in the MMA loop add ~130 cycles per k-block.
-#ifdef RL_TRACE
-#define RL_TRACE_N 256
-#define RL_STAMP(ev, idx)                                                               \
-  do {                                                                                  \
-    if (p.trace != nullptr && pair == 0 && (idx) < RL_TRACE_N && (!(p.debug & 64) || ((ev) == 2 && !(p.debug & 16)) || (ev) == 5)) \
-      p.trace[((int)rank * 8 + (ev)) * RL_TRACE_N + (idx)] = clock64();                 \
-  } while (0)
-#define RL_DEBUG(bit) ((p.debug & (bit)) != 0)
-// wall-clock (ns) stamps of the kernel's phases, CTA 0 only, behind the clock64 stamps
-#define RL_GSTAMP(i)                                                                         \
-  do {                                                                                       \
-    if (p.trace != nullptr && blockIdx.x == 0) {                                             \
-      p.trace[2 * 8 * RL_TRACE_N + (i)] = (long long)global_timer_ns();                      \
-      p.trace[2 * 8 * RL_TRACE_N + 8 + (i)] = clock64();                                     \
-    }                                                                                        \
-  } while (0)
-#else
-#define RL_GSTAMP(i) \
-  do {               \
-  } while (0)
-#define RL_STAMP(ev, idx) \
-  do {                    \
-  } while (0)
-#define RL_DEBUG(bit) false
+#ifndef RL_PAIR_PREFETCH
+#define RL_PAIR_PREFETCH 0
 #endif
 
-template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false, bool SWIGLU_ = false>
+template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false, bool SWIGLU_ = false,
+          bool FP8_ = false>
 struct PairCfg {
+  static constexpr int PREFETCH = RL_PAIR_PREFETCH;  // k-blocks the producer's L2 prefetch runs ahead of its loads (0 = off)
   static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_, ASLOTS = ASLOTS_, TG = TG_, AMODE = AMODE_;
   // PRESTATS: 1/rms per token comes from rowstats_kernel; the transform warps only fold gamma
   static constexpr bool PRESTATS = PRESTATS_;
@@ -75,6 +45,17 @@ struct PairCfg {
   // [128,256) hold gate and up of the same 128 output channels and the epilogue emits silu(gate) * up.
   static constexpr bool SWIGLU = SWIGLU_;
   static_assert(!SWIGLU_ || (BN_ == 256 && NACC_ == 1), "SwiGLU epilogue: 256-column tile, one accumulator");
+  // FP8: both operands are e4m3 (activations quantised per token by rowquant_kernel, weights with per-channel
+  // scales), k-blocks of 128 elements (the same 128 bytes per tile row), kind::f8f6f4 MMAs, and the epilogue
+  // multiplies by row_scale[m] * w_scale[n].
+  static constexpr bool FP8 = FP8_;
+  static constexpr int KBW = FP8_ ? 128 : 64;  // elements per k-block
+  // XFORM: the kernel has transform warps (they fold gamma and / or accumulate the sums of squares).  Without
+  // them (x straight from shared memory, 1/rms from the pre-pass) both operand tiles complete directly on the
+  // barrier the MMA warp waits on and the CTA is producer + MMA + epilogue only.
+  static constexpr bool XFORM = (AMODE_ == A_TS_FOLD) || !PRESTATS_;
+  static_assert(XFORM ? (TG_ > 0) : (TG_ == 0), "transform groups exactly where there is transform work");
+  static_assert(!FP8_ || (!XFORM && !SWIGLU_ && BN_ == 256), "FP8: operands straight from shared memory");
   static constexpr int THREADS = 64 + 128 * TG + 128;
   static constexpr int A_BYTES = 128 * 64 * 2;
   static constexpr int B_BYTES = (BN / 2) * 64 * 2;  // this CTA's half of the W tile
@@ -85,7 +66,8 @@ struct PairCfg {
   static constexpr int OFF_EPI = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_G = OFF_EPI + 2 * EPI_BYTES;
   static constexpr int OFF_RS = OFF_G + (AMODE_ == A_TS_FOLD ? STAGES * G_BYTES : 0);
-  static constexpr int OFF_BAR = OFF_RS + (PRESTATS_ ? 0 : TG * NACC * 128 * 4);
+  static constexpr int OFF_WS = OFF_RS + (PRESTATS_ ? 0 : TG * NACC * 128 * 4);  // FP8: [2][256] w_scale of the tiles being drained
+  static constexpr int OFF_BAR = OFF_WS + (FP8_ ? 2 * 256 * 4 : 0);
   static constexpr int NUM_BARS = 3 * STAGES + 4 * NACC;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64;  // no alignment slack: the kernel checks the base instead
@@ -97,7 +79,8 @@ struct PairCfg {
   static_assert(NACC == 1 || NACC == 2, "NACC");
   // a ring slot is always served by the same transform group (parity waits alias otherwise), and a
   // group that waits for the MMA which last read its A slot must itself be the one feeding that MMA
-  static_assert(STAGES % TG == 0 && (AMODE != A_TS_FOLD || (STAGES - ASLOTS) % TG == 0), "ring / group layout");
+  static_assert(TG == 0 || (STAGES % (TG ? TG : 1) == 0 && (AMODE != A_TS_FOLD || (STAGES - ASLOTS) % (TG ? TG : 1) == 0)),
+                "ring / group layout");
   static_assert(AMODE != A_TS_FOLD || (ASLOTS <= STAGES && NACC * BN + 32 * ASLOTS <= 512), "TMEM budget");
   static_assert(NACC * BN <= 512, "TMEM budget");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -142,12 +125,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
   constexpr bool PRESTATS = Cfg::PRESTATS;
   constexpr bool SWIGLU = Cfg::SWIGLU;
+  constexpr bool FP8 = Cfg::FP8, XFORM = Cfg::XFORM;
+  constexpr int KBW = Cfg::KBW;
   // k-split tail tiles: 1/rms must come from outside (a slice sees only part of a row) and the epilogue is plain
   constexpr bool TAIL = PRESTATS && !SWIGLU && BN == 256;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
-  if (threadIdx.x == 0) RL_GSTAMP(0);
   if (sbase & 1023u) {
     // swizzled tiles need a 1024-byte aligned base; every thread of both CTAs sees the same value
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)DEV_BAD_SMEM_ALIGNMENT);
@@ -166,6 +150,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
   float* rs = reinterpret_cast<float*>(smem + Cfg::OFF_RS);  // [TG][NACC][128] partial sums of squares
+  [[maybe_unused]] float* wsc = reinterpret_cast<float*>(smem + Cfg::OFF_WS);  // FP8: [2][256] per-channel scales
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
@@ -173,7 +158,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   // p.extra_kb k-blocks are appended to every tile's k-loop with their operands taken from a second pair of
   // matrices (tm_x2 [M, L], tm_w2 [N, L], columns beyond L zero-filled by TMA): y = x W^T + x2 W2^T, the low-rank
   // update of a LoRA layer riding in the same accumulator.  Only the producer knows the difference.
-  const int KB_main = (p.K + 63) >> 6;
+  const int KB_main = (p.K + KBW - 1) / KBW;
   const int KB = KB_main + p.extra_kb;
   const int total_tiles = p.m_tiles * p.n_tiles;  // 256 x BN tiles
   const bool has_gamma = (p.gamma != nullptr);
@@ -181,13 +166,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_fullA(s), 1);
-      mbar_init(bar_ready(s), 2 + 8);
+      mbar_init(bar_ready(s), XFORM ? 2 + 8 : 2);
       mbar_init(bar_empty(s), 1);
     }
     for (int a = 0; a < NACC; ++a) {
       mbar_init(bar_tfull(a), 1);
       mbar_init(bar_tempty(a), 8);
-      mbar_init(bar_rsfull(a), 4 * TG);
+      mbar_init(bar_rsfull(a), XFORM ? 4 * TG : 1);
       mbar_init(bar_rsfree(a), 4);
     }
     mbar_init(bar_tail, 1);
@@ -212,45 +197,75 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) RL_GSTAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs, own halves)
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    [[maybe_unused]] int jp = 0;
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
     PairItem w;
+    // L2 prefetch PF k-blocks ahead of the loads.  The ring holds at most STAGES k-blocks in flight, which covers
+    // an L2 hit but not a trip to DRAM (the first touch of every operand tile): a stage that waits on DRAM stalls
+    // the in-order ring behind it.  The prefetch takes that trip early, without holding a stage.
+    constexpr int PF = Cfg::PREFETCH;
+    auto prefetch_kb = [&](int mt_, int nt_, int kbt) {
+      const bool extra = (kbt >= KB_main);
+      const int kcol = extra ? (kbt - KB_main) * KBW : kbt * KBW;
+      tma_prefetch_l2_2d(extra ? &tm_x2 : &tm_x, kcol, mt_ * 256 + (int)rank * 128);
+      tma_prefetch_l2_2d(extra ? &tm_w2 : &tm_w, kcol, SWIGLU ? (int)rank * p.N + nt_ * 128 : nt_ * BN + (int)rank * (BN / 2));
+    };
+    // FP8: the quantised activations are written by the kernel launched just before this one
+    if (FP8) grid_dependency_wait();
     for (int i = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i, w); ++i) {
       int mt, nt;
       prefill_tile_coords(w.t, p, mt, nt);
+      [[maybe_unused]] PairItem wn;
+      [[maybe_unused]] int mtn = 0, ntn = 0;
+      [[maybe_unused]] bool have_next = false;
+      if (PF > 0) {
+        have_next = pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i + 1, wn);
+        if (have_next) prefill_tile_coords(wn.t, p, mtn, ntn);
+        if (i == 0 && elect_one())
+          for (int kb = w.kb0; kb < min(w.kb0 + PF, w.kb1); ++kb) prefetch_kb(mt, nt, kb);
+        __syncwarp();
+      }
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
         if (elect_one()) {
-          RL_STAMP(0, jp);
+          if (PF > 0) {
+            const int kbt = kb + PF;
+            if (kbt < w.kb1) prefetch_kb(mt, nt, kbt);
+            else if (have_next && wn.kb0 + (kbt - w.kb1) < wn.kb1) prefetch_kb(mtn, ntn, wn.kb0 + (kbt - w.kb1));
+          }
           const bool extra = (kb >= KB_main);
-          const int kvalid = min(64, p.K - kb * 64);
-          const uint32_t gbytes = (TS && has_gamma && !extra) ? (uint32_t)kvalid * 2u : 0u;
-          const int kcol = extra ? (kb - KB_main) * 64 : kb * 64;
-          mbar_expect_tx(bar_fullA(s), Cfg::A_BYTES + gbytes);
-          tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, extra ? &tm_x2 : &tm_x, bar_fullA(s), kcol,
-                      mt * 256 + (int)rank * 128);
-          if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_fullA(s));
+          const int kcol = extra ? (kb - KB_main) * KBW : kb * KBW;
           const uint32_t lead_ready = lead_ready0 + 8u * s;
-          mbar_expect_tx_cluster(lead_ready, Cfg::B_BYTES);
+          if (XFORM) {
+            const int kvalid = min(64, p.K - kb * 64);
+            const uint32_t gbytes = (TS && has_gamma && !extra) ? (uint32_t)kvalid * 2u : 0u;
+            mbar_expect_tx(bar_fullA(s), Cfg::A_BYTES + gbytes);
+            tma_load_2d(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, extra ? &tm_x2 : &tm_x, bar_fullA(s), kcol,
+                        mt * 256 + (int)rank * 128);
+            if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_fullA(s));
+            mbar_expect_tx_cluster(lead_ready, Cfg::B_BYTES);
+          } else {
+            // no transform stage: the x tile is counted on the MMA warp's barrier as well
+            mbar_expect_tx_cluster(lead_ready, Cfg::A_BYTES + Cfg::B_BYTES);
+            tma_load_2d_pair(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, extra ? &tm_x2 : &tm_x, lead_ready, kcol,
+                             mt * 256 + (int)rank * 128);
+          }
           tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, extra ? &tm_w2 : &tm_w, lead_ready, kcol,
                            SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
         }
         __syncwarp();
-        ++jp;
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer (rank 0 only)
     if (rank == 0) {
-      constexpr uint32_t idesc = make_idesc(256, BN, 1, 1);
+      constexpr uint32_t idesc = FP8 ? make_idesc(256, BN, 0, 0) : make_idesc(256, BN, 1, 1);
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       const uint64_t bdesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_B);
       const uint64_t adesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_A);
@@ -262,7 +277,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const int acc = (NACC == 2) ? (it & 1) : 0;
         const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
         if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1u, ctl, 1, 3 * STAGES + NACC + acc, it)) break;
-        if (lane == 0) RL_STAMP(5, it);
         const uint32_t d = tmem_base + acc * BN;
         // The issue loop sets the tensor cores' pace: one barrier wait per k-block, the poll for the
         // next slot started before this slot's MMAs are issued, and one predicated issue block.
@@ -271,8 +285,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           if (!ready_now) {
             if (!mbar_wait(bar_ready(s), ph, ctl, 1, STAGES + s, kb)) { ok = false; break; }
           }
-          if (lane == 0) RL_STAMP(2, it * KB + kb - w.kb0);
-          if (lane == 0 && it == 0 && kb == w.kb0) RL_GSTAMP(2);
           tc_fence_after();
           const int sn = (s + 1 == STAGES) ? 0 : s + 1;
           const uint32_t phn = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
@@ -280,6 +292,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           if (TS) {
             umma_kblock_ts_pair(d, tmem_base + Cfg::A_COL0 + aslot * 32, bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)),
                                 idesc, (uint32_t)(kb != w.kb0), bar_empty(s), leader);
+          } else if (FP8) {
+            umma_kblock_f8_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
+                                   bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != w.kb0),
+                                   bar_empty(s), leader);
           } else {
             umma_kblock_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
                                 bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != w.kb0), bar_empty(s),
@@ -294,8 +310,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp < 2 + 4 * TG) {
+  } else if (XFORM && warp < 2 + 4 * TG) {
     // ------------------------------------------------------------ transform (both CTAs)
+    constexpr int TGd = TG ? TG : 1;  // (TG == 0 only in configurations without this role)
     const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -308,7 +325,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       const int acc = (NACC == 2) ? (it & 1) : 0;
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
       float2 ss2 = make_float2(0.f, 0.f);
-      for (int kb = w.kb0 + (grp - j_base % TG + TG) % TG; kb < w.kb1; kb += TG) {
+      for (int kb = w.kb0 + (grp - j_base % TGd + TGd) % TGd; kb < w.kb1; kb += TGd) {
         const int j = j_base + kb - w.kb0;
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
@@ -320,12 +337,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (q == 0 && lane == 0) RL_STAMP(3, j);
-        if ((!TS && PRESTATS) || RL_DEBUG(1)) {  // nothing to fold and nothing to sum: just hand the slot on
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(lead_ready0 + 8u * s);
-          continue;
-        }
         const uint8_t* a_row = smem + Cfg::OFF_A + s * Cfg::A_BYTES + row * 128;
         uint32_t v[32];
 #pragma unroll
@@ -370,16 +381,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
               }
             }
           }
-#ifdef RL_TRACE
-          if (q == 0 && lane == 0 && p.trace != nullptr && pair == 0 && j < RL_TRACE_N && !(p.debug & 64)) {
-            long long tck;  // ordered behind the multiplies (so behind the shared-memory loads) by a fake operand
-            uint32_t fold = 0;
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) fold ^= v[jj];
-            asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(fold));
-            p.trace[((int)rank * 8 + 1) * RL_TRACE_N + j] = tck;
-          }
-#endif
           __syncwarp();
           tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::A_COL0 + (j % ASLOTS) * 32, v);
           tmem_wait_st();
@@ -387,7 +388,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lead_ready0 + 8u * s);
-        if (q == 0 && lane == 0) RL_STAMP(4, j);
       }
       if (!ok) break;
       if (!PRESTATS) {
@@ -415,6 +415,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       prefill_tile_coords(w.t, p, mt, nt);
       const int acc = (NACC == 2) ? (it & 1) : 0;
       const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      [[maybe_unused]] const float* wc_tile = wsc + (it & 1) * 256;
+      if (FP8) {
+        // stage this tile's 256 per-channel scales while the accumulator is still filling; the buffer of the
+        // tile before last is free: every epilogue thread has passed this iteration's predecessor's barriers
+        const int n = nt * BN + epi_tid;
+        wsc[(it & 1) * 256 + epi_tid] = (n < p.N) ? __ldg(p.w_scale + n) : 0.f;
+        wsc[(it & 1) * 256 + 128 + epi_tid] = (n + 128 < p.N) ? __ldg(p.w_scale + n + 128) : 0.f;
+      }
       float r_pre = 0.f;
       if (PRESTATS) {
         // launched with programmatic stream serialisation right behind rowstats_kernel: everything up to
@@ -431,7 +439,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       named_bar_sync(4, 128);
       ok = (*epi_go != 0);
       if (!ok) break;
-      if (epi_tid == 0) RL_STAMP(6, it);
       tc_fence_after();
       float r = r_pre;
       if (!PRESTATS) {
@@ -443,10 +450,20 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (lane == 0) mbar_arrive(bar_rsfree(acc));
       }
       // convert 32 accumulator columns to bf16: 16 packed words
-      auto cvt32 = [&](const uint32_t (&v)[32], uint32_t (&o)[16]) {
+      // (col = first of the 32 columns within the tile; FP8 also applies the per-channel weight scales)
+      auto cvt32 = [&](const uint32_t (&v)[32], uint32_t (&o)[16], [[maybe_unused]] int col) {
+        if constexpr (FP8) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          o[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * r, __uint_as_float(v[2 * j + 1]) * r);
+          for (int j = 0; j < 8; ++j) {
+            const float4 ws4 = *reinterpret_cast<const float4*>(wc_tile + col + 4 * j);
+            o[2 * j] = pack_bf16x2(__uint_as_float(v[4 * j]) * r * ws4.x, __uint_as_float(v[4 * j + 1]) * r * ws4.y);
+            o[2 * j + 1] = pack_bf16x2(__uint_as_float(v[4 * j + 2]) * r * ws4.z, __uint_as_float(v[4 * j + 3]) * r * ws4.w);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            o[j] = pack_bf16x2(__uint_as_float(v[2 * j]) * r, __uint_as_float(v[2 * j + 1]) * r);
+        }
       };
       // write 64 columns (two 16-word halves) of this thread's row into a swizzled staging tile
       auto sts64 = [&](uint8_t* stage, const uint32_t (&lo)[16], const uint32_t (&hi)[16]) {
@@ -563,7 +580,15 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 }
               }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) o[qq >> 1][(qq & 1) * 8 + j] = pack_bf16x2(a[2 * j] * r, a[2 * j + 1] * r);
+              for (int j = 0; j < 8; ++j) {
+                float s0 = r, s1 = r;
+                if constexpr (FP8) {
+                  const float2 ws2 = *reinterpret_cast<const float2*>(wc_tile + (c_lo + c) * 64 + qq * 16 + 2 * j);
+                  s0 *= ws2.x;
+                  s1 *= ws2.y;
+                }
+                o[qq >> 1][(qq & 1) * 8 + j] = pack_bf16x2(a[2 * j] * s0, a[2 * j + 1] * s1);
+              }
             }
             sts64(stage, o[0], o[1]);
             fence_proxy_async_smem();
@@ -633,18 +658,17 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           tmem_wait_ld();
           if (c < 2) {
             uint32_t lo[16], hi[16];
-            cvt32(v0, lo);
-            cvt32(v1, hi);
+            cvt32(v0, lo, c * 64);
+            cvt32(v1, hi, c * 64 + 32);
             sts64(c == 0 ? stage0 : stage1, lo, hi);
           } else {
-            cvt32(v0, pk[2 * (c - 2)]);
-            cvt32(v1, pk[2 * (c - 2) + 1]);
+            cvt32(v0, pk[2 * (c - 2)], c * 64);
+            cvt32(v1, pk[2 * (c - 2) + 1], c * 64 + 32);
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
-        if (epi_tid == 0) RL_STAMP(7, it);
         fence_proxy_async_smem();
         named_bar_sync(2, 128);
         const int m0 = mt * 256 + (int)rank * 128;
@@ -679,11 +703,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
-            if (epi_tid == 0) RL_STAMP(7, it);
           }
           uint32_t lo[16], hi[16];
-          cvt32(v0, lo);
-          cvt32(v1, hi);
+          cvt32(v0, lo, c * 64);
+          cvt32(v1, hi, c * 64 + 32);
           sts64(stage, lo, hi);
           fence_proxy_async_smem();
           named_bar_sync(2, 128);
@@ -695,9 +718,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
       }
     }
-    if (epi_tid == 0) RL_GSTAMP(3);
     if (epi_tid == 0) tma_store_wait_all<0>();
-    if (epi_tid == 0) RL_GSTAMP(4);
   }
 
   // ------------------------------------------------------------ teardown
@@ -713,7 +734,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
-  if (threadIdx.x == 32) RL_GSTAMP(5);
 }
 
 }  // namespace rl

@@ -177,14 +177,21 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // launch_dependents: the next kernel in the stream (if it was launched with programmatic stream
 // serialisation) may start its prologue once every CTA of this grid has got here or exited.
 // grid_dependency_wait: returns once all grids this one depends on have completed and their memory
-// is visible; a no-op for a normally launched kernel.  Nothing that another kernel may have written
-// or may still read is touched before it.
+// is visible; a no-op for a normally launched kernel.  A kernel launched with the programmatic
+// attribute must not touch, before this wait, anything the previous kernel in the stream may still
+// write; the host side only sets the attribute where that holds.
 __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+// Ask for the box at (x, y) of a 2-D tiled tensor to be brought into L2.  No completion to wait for: a later
+// TMA load of the same box then finds it there (or joins the fill in flight) instead of paying DRAM latency
+// while it holds a shared-memory stage.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 // 2-D tiled load global -> shared, completion on an mbarrier of this CTA.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {

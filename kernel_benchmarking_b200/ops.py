@@ -65,6 +65,23 @@ def _check_matrix(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
         raise ValueError(f"{name} must be row-major with unit stride along its last dimension")
 
 
+def _check_gamma(gamma: Optional[torch.Tensor], x: torch.Tensor, K: int) -> None:
+    if gamma is None:
+        return
+    if not isinstance(gamma, torch.Tensor) or not gamma.is_cuda or gamma.device != x.device or gamma.dtype != torch.bfloat16:
+        raise ValueError("gamma must be a bf16 CUDA tensor on x's device")
+    if gamma.dim() != 1 or gamma.shape[0] != K or gamma.stride(0) != 1:
+        raise ValueError(f"gamma must be a contiguous vector of length K={K}")
+
+
+def _check_out(out: torch.Tensor, M: int, N: int, like: torch.Tensor) -> None:
+    """A caller-supplied output: the kernel's TMA store is laid out from M and N, not from the buffer, so a
+    smaller buffer or one on another device would be written out of bounds."""
+    _check_matrix("out", out, torch.bfloat16)
+    if tuple(out.shape) != (M, N) or out.device != like.device:
+        raise ValueError(f"out must be [{M}, {N}] on the inputs' device, got {tuple(out.shape)} on {out.device}")
+
+
 def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tensor, eps: float = 1e-6, *,
                    w_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                    variant: str | int = "auto") -> torch.Tensor:
@@ -95,11 +112,7 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
         raise ValueError(f"x is [M, {K}] but W is [N, {K2}]: inner dimensions differ")
     if W.device != x.device:
         raise ValueError("x and W must be on the same device")
-    if gamma is not None:
-        if not gamma.is_cuda or gamma.device != x.device or gamma.dtype != torch.bfloat16:
-            raise ValueError("gamma must be a bf16 CUDA tensor on x's device")
-        if gamma.dim() != 1 or gamma.shape[0] != K or gamma.stride(0) != 1:
-            raise ValueError(f"gamma must be a contiguous vector of length K={K}")
+    _check_gamma(gamma, x, K)
     if M == 0 or N == 0:
         return torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     if out is None:
@@ -107,9 +120,7 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
         buf = torch.empty((M, ldy), dtype=torch.bfloat16, device=x.device)
         out = buf if ldy == N else buf[:, :N]
     else:
-        _check_matrix("out", out, torch.bfloat16)
-        if tuple(out.shape) != (M, N) or out.device != x.device:
-            raise ValueError(f"out must be [{M}, {N}] on x's device")
+        _check_out(out, M, N, x)
     v = _lib.VARIANTS[variant] if isinstance(variant, str) else int(variant)
     lib = _lib.load()
     stream = _stream_ptr(x.device)
@@ -143,12 +154,11 @@ def rmsnorm_swiglu(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
     if K2 != K or W.device != x.device or N2 % 2:
         raise ValueError("W must be [2n, K] on x's device")
     N = N2 // 2
-    if gamma is not None and (not gamma.is_cuda or gamma.dtype != torch.bfloat16 or gamma.shape != (K,)):
-        raise ValueError("gamma must be a bf16 CUDA vector of length K")
+    _check_gamma(gamma, x, K)
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     else:
-        _check_matrix("out", out, torch.bfloat16)
+        _check_out(out, M, N, x)
     if M == 0:
         return out
     lib = _lib.load()
@@ -176,7 +186,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = N
         buf = torch.empty((M, ldc), dtype=torch.bfloat16, device=a.device)
         out = buf if ldc == N else buf[:, :N]
     else:
-        _check_matrix("out", out, torch.bfloat16)
+        _check_out(out, M, N, a)
     if M == 0 or N == 0:
         return out
     stream = _stream_ptr(a.device)
@@ -208,9 +218,7 @@ def lora_linear(a: torch.Tensor, b: torch.Tensor, lA: torch.Tensor, lB: torch.Te
         buf = torch.empty((M, ldy), dtype=torch.bfloat16, device=a.device)
         out = buf if ldy == N else buf[:, :N]
     else:
-        _check_matrix("out", out, torch.bfloat16)
-        if tuple(out.shape) != (M, N) or out.device != a.device:
-            raise ValueError(f"out must be [{M}, {N}] on a's device")
+        _check_out(out, M, N, a)
     if M == 0 or N == 0:
         return out
     xa = gemm_nt(a, lA)
@@ -261,14 +269,24 @@ def row_stats(x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float = 1e-6,
 
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronise and raise if any kernel launched through this module recorded a device-side
-    timeout.  Kept out of `rmsnorm_linear` so the hot call never synchronises."""
+    timeout.  Kept out of `rmsnorm_linear` so the hot call never synchronises.
+
+    A kernel that gave up a wait may leave tile counters of its workspace non-zero, and every later call on
+    that workspace would then be wrong: the workspace is cleared again before the error is raised, so the
+    caller can go on after handling it."""
     lib = _lib.load()
-    for (dev, _stream), ws in list(_workspaces.items()):
+    first_error = None
+    for (dev, stream), ws in list(_workspaces.items()):
         if device is not None and torch.device(device).index not in (None, dev):
             continue
         detail = (ctypes.c_int * 8)()
         with torch.cuda.device(dev):
             torch.cuda.synchronize()
             rc = lib.rl_read_status(ws.data_ptr(), detail)
-        if rc != _lib.RL_OK:
-            raise RuntimeError(f"rmsnorm_linear: {_lib.error_string(rc)}; detail={list(detail)}")
+            if rc != _lib.RL_OK:
+                _lib.check(lib.rl_workspace_init(ws.data_ptr(), ws.numel(), stream), "rl_workspace_init")
+                torch.cuda.synchronize()
+                if first_error is None:
+                    first_error = f"rmsnorm_linear: {_lib.error_string(rc)}; detail={list(detail)}"
+    if first_error is not None:
+        raise RuntimeError(first_error)

@@ -346,7 +346,8 @@ def test_row_statistics(M, K, has_gamma):
     assert none is None and torch.equal(only_rms, inv_rms)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 2048), (1000, 1032, 4096), (5, 264, 1024)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 2048), (1000, 1032, 4096), (5, 264, 1024),
+                                   (300, 520, 272), (512, 264, 1040), (64, 136, 16)])   # K not a multiple of 128
 def test_fp8_shapes(M, N, K):
     x, gm, W = orc.make_inputs(M, N, K, seed=M + N)
     Wq, w_scale = orc.quantize_weight_e4m3(W)
@@ -356,6 +357,48 @@ def test_fp8_shapes(M, N, K):
     assert orc.rel_max_err(y, ref) <= (FP8_TOL if K >= 4096 else FP8_TOL_SMALL_K)
     # the kernels follow the oracle's arithmetic model to bf16 rounding
     assert orc.rel_max_err(y, orc.fp8_kernel_model(x, gm, Wq, w_scale, 1e-6).float()) <= 1e-2
+
+
+def test_fp8_strided_operands():
+    """x and Wq as column slices of wider buffers (ldx > K, ldw > K), K not a multiple of the 128-element k-block."""
+    for (M, N, K) in [(300, 520, 1040), (200, 264, 2048)]:
+        x, gm, W = orc.make_inputs(M, N, K, seed=M + K)
+        Wq, w_scale = orc.quantize_weight_e4m3(W)
+        xb = torch.full((M, K + 64), 3.0, dtype=torch.bfloat16, device=DEV)
+        Wb = torch.full((N, K + 128), 1.0, dtype=torch.bfloat16, device=DEV).to(torch.float8_e4m3fn)
+        xb[:, :K] = x.to(DEV)
+        Wb.view(torch.uint8)[:, :K] = Wq.view(torch.uint8).to(DEV)
+        y = kb.rmsnorm_linear(xb[:, :K], gm.to(DEV), Wb[:, :K], 1e-6, w_scale=w_scale.to(DEV))
+        torch.cuda.synchronize()
+        kb.check_status()
+        ref = orc.reference_fp32(x, gm, Wq, 1e-6, w_scale=w_scale)
+        assert orc.rel_max_err(y.cpu(), ref) <= (FP8_TOL if K >= 4096 else FP8_TOL_SMALL_K)
+        assert orc.rel_max_err(y.cpu(), orc.fp8_kernel_model(x, gm, Wq, w_scale, 1e-6).float()) <= 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 4096), (2560, 4096, 4096), (8192, 1792, 4096)])
+def test_fp8_tail_tiles_split_along_k(M, N, K):
+    """The FP8 kernel cuts the tiles of a partly filled last round along K like the bf16 kernel does: same results
+    as whole tiles to one bf16 ulp, identical from run to run.  The last shape is one of eight column shards of
+    the FP8 benchmark configuration (224 tiles on 74 pairs: two tiles left for a fourth round)."""
+    import ctypes
+    a, b = ctypes.c_int(), ctypes.c_int()
+    _lib.check(_lib.load().rl_plan_tail_split(M, N, K // 2, 74, ctypes.byref(a), ctypes.byref(b)), "plan")  # K/128 k-blocks
+    assert a.value > 0 and b.value >= 2
+    x, gm, W = orc.make_inputs(M, N, K, seed=M + N)
+    Wq, w_scale = orc.quantize_weight_e4m3(W)
+    xd, gd, Wqd, wsd = x.to(DEV), gm.to(DEV), Wq.to(DEV), w_scale.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd)
+    yw = kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd, variant="auto_whole")
+    torch.cuda.synchronize()
+    kb.check_status()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:32]
+    ref = orc.reference_fp32(x[rows], gm, Wq, 1e-6, w_scale=w_scale)
+    assert orc.rel_max_err(y.cpu()[rows], ref) <= FP8_TOL_SMALL_K      # a row sample's own maximum is a noisy denominator
+    assert orc.rel_max_err(y.cpu()[rows], orc.fp8_kernel_model(x[rows], gm, Wq, w_scale, 1e-6).float()) <= 1e-2
+    assert orc.rel_max_err(y, yw.float()) <= ONE_ULP
+    for _ in range(3):
+        assert torch.equal(kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd), y)
 
 
 def test_config5_fp8_weights():
@@ -504,14 +547,105 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert orc.rel_max_err(run(x, gm, W, 1e-6), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
 
 
+def test_chained_calls_need_no_synchronise_between_them():
+    """A small-M call (whose kernel lets its successor start early) feeding the plain GEMM and the LoRA linear,
+    back to back on one stream: the consumers must see the finished y, as if a synchronise stood between."""
+    M, N, K, N2 = 16, 1024, 512, 768
+    x, gm, W = orc.make_inputs(M, N, K, seed=7)
+    g = torch.Generator().manual_seed(8)
+    W2 = (torch.randn(N2, N, generator=g) * N ** -0.5).bfloat16().to(DEV)
+    lA = (torch.randn(16, N, generator=g) * N ** -0.5).bfloat16().to(DEV)
+    lB = torch.randn(N2, 16, generator=g).bfloat16().to(DEV)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    xpad = torch.zeros(256, K, dtype=torch.bfloat16, device=DEV)
+    xpad[:M] = xd
+    # reference chain with a synchronise after every call
+    y1 = kb.rmsnorm_linear(xpad, gd, Wd, 1e-6)
+    torch.cuda.synchronize()
+    z_ref = kb.gemm_nt(y1, W2)
+    torch.cuda.synchronize()
+    l_ref = kb.lora_linear(y1, W2, lA, lB)
+    torch.cuda.synchronize()
+    ysm = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    torch.cuda.synchronize()
+    zs_ref = kb.gemm_nt(ysm, W2)
+    torch.cuda.synchronize()
+    y_buf, ysm_buf = torch.empty_like(y1), torch.empty_like(ysm)
+    for _ in range(50):
+        y_buf.zero_()
+        ysm_buf.zero_()
+        kb.rmsnorm_linear(xpad, gd, Wd, 1e-6, out=y_buf)
+        z = kb.gemm_nt(y_buf, W2)
+        lo = kb.lora_linear(y_buf, W2, lA, lB)
+        kb.rmsnorm_linear(xd, gd, Wd, 1e-6, out=ysm_buf)      # small-M kernel: triggers its dependents early
+        zs = kb.gemm_nt(ysm_buf, W2)
+        assert torch.equal(z, z_ref) and torch.equal(lo, l_ref) and torch.equal(zs, zs_ref)
+    kb.check_status()
+
+
+def test_bad_output_buffers_raise():
+    """A caller-supplied `out` of the wrong shape or on the wrong device must be refused on the host: the kernel's
+    store is laid out from M and N and would write past a smaller buffer."""
+    x, gm, W = orc.make_inputs(256, 256, 64, seed=1)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    small = torch.empty(128, 256, dtype=torch.bfloat16, device=DEV)
+    for call in (lambda: kb.rmsnorm_linear(xd, gd, Wd, 1e-6, out=small),
+                 lambda: kb.gemm_nt(xd, Wd, out=small),
+                 lambda: kb.rmsnorm_swiglu(xd, gd, Wd, 1e-6, out=small),
+                 lambda: kb.rmsnorm_swiglu(xd, gd, Wd, 1e-6, out=torch.empty(256, 256, dtype=torch.bfloat16, device=DEV)),
+                 lambda: kb.rmsnorm_swiglu(xd, gd[:32], Wd, 1e-6),
+                 lambda: kb.rmsnorm_swiglu(xd, gd.float(), Wd, 1e-6),
+                 lambda: kb.gemm_nt(xd, Wd, out=torch.empty(256, 256, dtype=torch.bfloat16))):
+        with pytest.raises(ValueError):
+            call()
+
+
+def test_status_check_clears_the_workspace_after_a_timeout():
+    """check_status() raises on a recorded device-side timeout and leaves the workspace clean, so the next call
+    on the same stream works and reports nothing."""
+    from kernel_benchmarking_b200 import ops
+    x, gm, W = orc.make_inputs(16, 256, 128, seed=3)
+    ref = orc.reference_fp32(x, gm, W, 1e-6)
+    assert orc.rel_max_err(run(x, gm, W, 1e-6), ref) <= BF16_TOL         # makes sure this stream has a workspace
+    stream = ops._stream_ptr(torch.device(DEV))
+    ws = ops._workspaces[(0, stream)]
+    lib = _lib.load()
+    ws[256:256 + 64].fill_(1)                                             # a counter left non-zero, as after a timeout
+    assert lib.rl_selftest_wait_timeout(ws.data_ptr(), ws.numel(), 2_000_000, stream) == _lib.RL_OK
+    with pytest.raises(RuntimeError):
+        kb.check_status()
+    kb.check_status()                                                     # clean again
+    assert int(ws[:4096].to(torch.int32).sum()) == 0
+    assert orc.rel_max_err(run(x, gm, W, 1e-6), ref) <= BF16_TOL
+
+
+def test_auto_whole_never_splits_and_matches():
+    """`variant="auto_whole"`: the kernels AUTO picks, every tile computed whole (no CTA waits for another)."""
+    for (M, N, K, has_gamma) in [(4096, 1536, 7168, True), (512, 1024, 4096, False), (8, 1024, 512, True)]:
+        x, gm, W = orc.make_inputs(M, N, K, seed=5, gamma=has_gamma)
+        ya = run(x, gm, W, 1e-6)
+        yw = run(x, gm, W, 1e-6, variant="auto_whole")
+        assert orc.rel_max_err(yw, orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+        assert orc.rel_max_err(yw, ya.float()) <= ONE_ULP
+    lib = _lib.load()
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 1, 1)] == "prefill_pair_prestats"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 0, 1)] == "prefill_pair_direct_prestats"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(16, 28672, 4096, 1, 1)] == "decode"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(100, 512, 512, 1, 1)] == "prefill_ts_n192"
+
+
 @pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_column_parallel_two_gpus_nccl():
     """W split over two GPUs, x replicated, y assembled with one NCCL all-gather: equals the oracle."""
     import subprocess
     import sys as _sys
+    import socket
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_column_parallel_worker.py")
+    with socket.socket() as sock:          # a port nobody holds right now: two suites on one box do not collide
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     r = subprocess.run([_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29533", worker],
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), worker],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 
