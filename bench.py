@@ -1,31 +1,37 @@
 #!/usr/bin/env python
 """Benchmark of the fused RMSNorm -> Linear operator on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--no-extra]
 
 One step = one pass of the operator over one batch of seeded synthetic input.
-Default workload: the bf16 prefill QKV projection x [4096, 4096] @ W [6144, 4096]^T.
-With N > 1 (launched by torchrun, one rank per GPU) W is column-sharded: every
-rank holds its own [6144, 4096] block of a [6144 * N, 4096] weight, x is
-replicated, no collective on the data path (weak scaling).  Rank 0 prints ONE
-JSON line.
 
-  value     whole-job TFLOP/s (2 M N K per step), inputs resident in HBM, timed
-            with CUDA events on the launching stream, max over ranks
-  e2e       the same through the host-buffer call: pinned host x -> device,
-            kernel, y -> pinned host, all inside the timed region
-  roofline  the kernel's achieved TFLOP/s (or GB/s for the M <= 64 workloads)
-            against the measured peak of this GPU pool
-  cpu_baseline  the reference's torch path (rms_norm then matmul) on the host
-            cores, on a bounded row sample of the same workload
+Default workload, at every N: the bf16 prefill MLP gate+up layer x [16384, 8192] @ W [57344, 8192]^T with
+gamma, W split along N over the N ranks (strong scaling: the whole job is the same at every N; N = 1 runs
+the whole layer on one GPU), x replicated, no collective on the data path.  Launched by torchrun for
+N > 1, one rank per GPU.  Rank 0 prints ONE JSON line.
 
---impl reference times that CPU path alone, as the main value.
+  value       whole-job TFLOP/s (2 M N K per step over all ranks), inputs resident in HBM, CUDA events on
+              the launching stream, max over ranks; `--steps` steps are timed in each of 5 windows and the
+              median window is reported (all windows are listed)
+  e2e         the same through the host-buffer call: pinned host x -> device, kernel, y -> pinned host,
+              all inside the timed region
+  roofline    the kernel's achieved TFLOP/s (GB/s for the M <= 64 workloads) against the measured peak
+  parity      after the timed region every rank checks a seeded row sample of its y[:, n0:n1] against the
+              reference's torch path in fp32 on its GPU
+  extra       further workloads, each with its own ms_per_step and roofline: the prefill QKV projection
+              (4096 x 6144 x 4096), the M <= 64 sweep in GB/s, the 8192 x 14336 x 4096 shape with bf16 and
+              e4m3 weights and their ratio; at N > 1 the e4m3 layer split along N
+  cpu_baseline  the reference's torch path (rms_norm then matmul, fp32) on the host cores, on a bounded
+              row sample of the same workload (N = 1 only)
+
+--impl reference times that CPU path alone, on the same configuration and sample, as the main value.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -37,29 +43,33 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# name -> (M, N, K, bound).  "tensor": TFLOP/s against the bf16 tensor peak; "hbm": GB/s against copy bandwidth
+# name -> (M, N, K, bound, fp8).  "tensor": TFLOP/s against the bf16 tensor peak; "hbm": GB/s against copy
+# bandwidth.  N is the whole layer; with more than one rank it is split along N.
 WORKLOADS = {
-    "prefill_qkv_4096x6144x4096": (4096, 6144, 4096, "tensor"),
-    "decode_1x28672x4096": (1, 28672, 4096, "hbm"),
-    "decode_4x28672x4096": (4, 28672, 4096, "hbm"),
-    "decode_16x28672x4096": (16, 28672, 4096, "hbm"),
-    "decode_64x28672x4096": (64, 28672, 4096, "hbm"),
-    "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor"),
-    "mlp_shard4_16384x14336x8192": (16384, 14336, 8192, "tensor"),
-    "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor"),
-    "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor"),   # e4m3 weights + per-channel scales
-    # strong scaling: the weight is split along N over the ranks (N below is the whole layer)
-    "strong_mlp_16384x57344x8192": (16384, 57344, 8192, "tensor"),
-    "strong_fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor"),
+    "mlp_16384x57344x8192": (16384, 57344, 8192, "tensor", False),
+    "prefill_qkv_4096x6144x4096": (4096, 6144, 4096, "tensor", False),
+    "decode_1x28672x4096": (1, 28672, 4096, "hbm", False),
+    "decode_4x28672x4096": (4, 28672, 4096, "hbm", False),
+    "decode_16x28672x4096": (16, 28672, 4096, "hbm", False),
+    "decode_64x28672x4096": (64, 28672, 4096, "hbm", False),
+    "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor", False),
+    "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor", False),
+    "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor", True),   # e4m3 weights + per-channel scales
 }
-DEFAULT_WORKLOAD = "prefill_qkv_4096x6144x4096"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries (profiles/)
-NCU_TRAFFIC_BYTES = {
-    "prefill_qkv_4096x6144x4096": 164.4e6,     # profiles/prefill_pair_kernel_4096x6144x4096_bf16.md
-    "decode_16x28672x4096": 240.3e6,           # profiles/decode_kernel_16x28672x4096_bf16.md
-    "fp8w_8192x14336x4096": 465.0e6,           # profiles/fp8_pair_kernel_8192x14336x4096_e4m3.md (GEMM kernel only)
+DEFAULT_WORKLOAD = "mlp_16384x57344x8192"
+EXTRA_1GPU = ["prefill_qkv_4096x6144x4096", "decode_1x28672x4096", "decode_4x28672x4096", "decode_16x28672x4096",
+              "decode_64x28672x4096", "bf16_8192x14336x4096", "fp8w_8192x14336x4096"]
+EXTRA_MULTI = ["fp8w_8192x14336x4096"]
+# DRAM bytes (read + written) per launch of the dominant kernel, from one profiler capture each, keyed by the
+# kernel variant and the per-GPU shape it was captured on.  A run whose variant or shape is not listed reports null.
+MEASURED_DRAM_BYTES = {
+    ("prefill_pair_prestats", 4096, 6144, 4096): 164.4e6,
+    ("decode", 16, 28672, 4096): 240.3e6,
 }
 L2_BYTES = 126 * 1024 * 1024
+WINDOWS = 5
+EPS = 1e-6
+CPU_SAMPLE_ROWS = 256      # rows of the default workload the CPU legs run (both arms use the same sample)
 
 
 def algorithmic_bytes(M, N, K, fp8=False):
@@ -71,134 +81,9 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-
-
-class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
-
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index = index
-        self.samples = []
-        self.proc = None
-        self.thread = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
-
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.06)
-        self.proc.terminate()   # the exact process started above
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        clocks, reasons, mx = [], set(), None
-        for p in self.samples:
-            try:
-                clocks.append(float(p[0]))
-                mx = float(p[1])
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        # the busy half of the samples: idle samples before/after the region would drag the median down
-        busy = clocks[len(clocks) // 2:] if clocks else []
-        med = busy[len(busy) // 2] if busy else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
-
-
-def make_buffers(M, N, K, dev, sets, seed, fp8=False):
-    """`sets` independent (x, gamma, W, y) groups so that consecutive steps never find their inputs in L2."""
-    g = torch.Generator(device="cpu").manual_seed(seed)
-    out = []
-    for _ in range(sets):
-        x = torch.randn(M, K, generator=g, dtype=torch.float32).to(torch.bfloat16)
-        gamma = (1.0 + 0.1 * torch.randn(K, generator=g, dtype=torch.float32)).to(torch.bfloat16)
-        W = torch.empty(N, K, dtype=torch.bfloat16)
-        # W is large: generate in slabs to bound host memory
-        for n0 in range(0, N, 8192):
-            n1 = min(N, n0 + 8192)
-            W[n0:n1] = (torch.randn(n1 - n0, K, generator=g, dtype=torch.float32) * K ** -0.5).to(torch.bfloat16)
-        Wd, wsc = W.to(dev), None
-        if fp8:
-            # per-output-channel absmax / 448 scales, weights stored as e4m3 codes
-            wsc = (Wd.float().abs().amax(dim=1) / 448.0).clamp_min(1e-30)
-            Wd = (Wd.float() / wsc[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
-        out.append((x.to(dev), gamma.to(dev), Wd, torch.empty(M, N, dtype=torch.bfloat16, device=dev), x, wsc))
-    return out
-
-
-def cpu_reference_time(M, N, K, budget_s=15.0):
-    """The reference's torch path on the host cores, fp32, on a row sample sized to ~budget_s."""
-    from oracle import rmsnorm_linear_oracle as orc
-    torch.set_num_threads(os.cpu_count() or 1)
-    rows = min(M, 512)
-    x, gm, W = orc.make_inputs(rows, N, K, seed=18, dtype=torch.float32)
-    orc.torch_rmsnorm_linear(x, gm, W, 1e-6)   # warm-up
-    times = []
-    t_all = time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_all < budget_s and len(times) < 20):
-        t0 = time.perf_counter()
-        orc.torch_rmsnorm_linear(x, gm, W, 1e-6)
-        times.append(time.perf_counter() - t0)
-    times.sort()
-    med = times[len(times) // 2]
-    return rows, med, len(times)
-
-
-def run_reference_arm(args, rank):
-    if rank != 0:
-        return
-    M, N, K, bound = WORKLOADS[args.workload]
-    # all host cores (torchrun pins OMP_NUM_THREADS=1 for its workers; only rank 0 works here)
-    torch.set_num_threads(os.cpu_count() or 1)
-    # bounded sample per step: min(M, 512) rows of the workload, all N and K
-    from oracle import rmsnorm_linear_oracle as orc
-    rows = min(M, 512)
-    x, gm, W = orc.make_inputs(rows, N, K, seed=18, dtype=torch.float32)
-    for _ in range(max(args.warmup, 1)):
-        orc.torch_rmsnorm_linear(x, gm, W, 1e-6)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        orc.torch_rmsnorm_linear(x, gm, W, 1e-6)
-    dt = (time.perf_counter() - t0) / args.steps
-    if bound == "tensor":
-        value, unit = 2.0 * rows * N * K / dt / 1e12, "TFLOP/s"
-    else:
-        value, unit = (4 * rows * K + 4 * N * K + 4 * K + 4 * rows * N) / dt / 1e9, "GB/s"
-    cores = torch.get_num_threads()
-    sample = f"{rows} of {M} rows x all N={N}, K={K}, fp32, torch CPU ({cores} threads of {os.cpu_count()} cpus)"
-    print(json.dumps({
-        "impl": "reference", "metric": metric_name(bound), "value": value, "unit": unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def metric_name(bound):
@@ -206,20 +91,323 @@ def metric_name(bound):
             else "fused RMSNorm+Linear HBM GB/s at M<=64")
 
 
+class ClockSampler:
+    """Samples nvidia-smi clocks, utilisation, power and throttle reasons of one GPU while a timed region runs.
+    The SM clock reported is that of the samples taken under load (GPU utilisation >= 50 %, or, if the
+    utilisation counter lags behind a short region, power draw within 40 % of the highest seen): on a
+    power-capped part the loaded samples are the LOW clocks, so they cannot be picked by clock value."""
+
+    Q = ("clocks.sm,clocks.max.sm,utilization.gpu,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int, period_ms: int = 50):
+        self.index, self.period_ms = index, period_ms
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return self
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 8:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(self.period_ms / 1000.0 + 0.02)
+        self.proc.terminate()   # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        return summarize_clock_samples(self.samples)
+
+
+def summarize_clock_samples(samples):
+    rows, reasons, mx = [], set(), None
+    for p in samples:
+        try:
+            clk, mx_, util, power = float(p[0]), float(p[1]), float(p[2]), float(p[3])
+        except ValueError:
+            continue
+        mx = mx_
+        rows.append((clk, util, power))
+        for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[4:8]):
+            if v.lower().startswith("active"):
+                reasons.add(name)
+    loaded = [r for r in rows if r[1] >= 50.0]
+    how = "utilization.gpu >= 50"
+    if not loaded and rows:
+        pmax = max(r[2] for r in rows)
+        loaded = [r for r in rows if r[2] >= 0.6 * pmax]
+        how = "power.draw >= 0.6 x max"
+    clocks = sorted(r[0] for r in loaded)
+    return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_mhz_min": clocks[0] if clocks else None,
+            "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(rows), "samples_under_load": len(loaded),
+            "power_w_max": max((r[2] for r in rows), default=None), "loaded_by": how}
+
+
+def shard_range(N, world, rank):
+    from kernel_benchmarking_b200.sharding import shard_bounds
+    return shard_bounds(N, world, rank, multiple=256)
+
+
+def make_buffers(M, N, K, dev, sets, seed, fp8=False):
+    """`sets` independent (x, gamma, W, y, w_scale) groups, generated on the device from a seeded generator, so
+    that consecutive steps never find their inputs in L2."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    out = []
+    for _ in range(sets):
+        x = torch.randn(M, K, generator=g, dtype=torch.float32, device=dev).to(torch.bfloat16)
+        gamma = (1.0 + 0.1 * torch.randn(K, generator=g, dtype=torch.float32, device=dev)).to(torch.bfloat16)
+        W = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+        for n0 in range(0, N, 8192):       # slabs bound the fp32 temporaries
+            n1 = min(N, n0 + 8192)
+            W[n0:n1] = (torch.randn(n1 - n0, K, generator=g, dtype=torch.float32, device=dev) * K ** -0.5).to(torch.bfloat16)
+        wsc = None
+        if fp8:
+            # per-output-channel absmax / 448 scales, weights stored as e4m3 codes
+            wsc = (W.float().abs().amax(dim=1) / 448.0).clamp_min(1e-30)
+            W = (W.float() / wsc[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+        out.append((x, gamma, W, torch.empty(M, N, dtype=torch.bfloat16, device=dev), wsc))
+    return out
+
+
+def torch_reference_rows(x, gamma, W, wsc, rows, eps):
+    """The reference's torch path (rms_norm then matmul) in fp32 for a sample of rows, column slab by slab."""
+    import torch.nn.functional as F
+    torch.backends.cuda.matmul.allow_tf32 = False
+    xn = F.rms_norm(x[rows].float(), (x.shape[1],), weight=gamma.float(), eps=eps)
+    out = torch.empty(len(rows), W.shape[0], dtype=torch.float32, device=x.device)
+    for n0 in range(0, W.shape[0], 8192):
+        n1 = min(W.shape[0], n0 + 8192)
+        Wf = W[n0:n1].float()
+        if wsc is not None:
+            Wf = Wf * wsc[n0:n1, None]
+        out[:, n0:n1] = xn @ Wf.t()
+    return out
+
+
+def parity_check(bufs, eps, fp8):
+    """max |y - y_ref| / max |y_ref| over a seeded sample of 64 rows of this rank's y (all of its columns)."""
+    x, gamma, W, y, wsc = bufs
+    M = x.shape[0]
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1234))[:min(M, 64)].to(x.device)
+    ref = torch_reference_rows(x, gamma, W, wsc, rows, eps)
+    err = float((y[rows].float() - ref).abs().max() / ref.abs().max())
+    return err, (3e-2 if fp8 else 1e-2)
+
+
+def cpu_reference(M, N, K, rows, budget_s, steps=None, warmup=1):
+    """The reference's torch path on the host cores, fp32, on `rows` rows of the workload (all N, all K).  Returns
+    seconds per pass (median), passes, threads."""
+    from oracle import rmsnorm_linear_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)     # torchrun pins OMP_NUM_THREADS=1 for its workers
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(rows, K, generator=g, dtype=torch.float32)
+    gm = 1.0 + 0.1 * torch.randn(K, generator=g, dtype=torch.float32)
+    W = torch.empty(N, K, dtype=torch.float32)
+    for n0 in range(0, N, 8192):
+        W[n0:min(N, n0 + 8192)].normal_(0.0, K ** -0.5, generator=g)
+    for _ in range(max(warmup, 1)):
+        orc.torch_rmsnorm_linear(x, gm, W, EPS)
+    times, t_all = [], time.perf_counter()
+    while (steps is not None and len(times) < steps) or (
+            steps is None and (len(times) < 3 or (time.perf_counter() - t_all < budget_s and len(times) < 20))):
+        t0 = time.perf_counter()
+        orc.torch_rmsnorm_linear(x, gm, W, EPS)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), sum(times) / len(times), len(times), torch.get_num_threads()
+
+
+def cpu_sample_rows(workload):
+    M = WORKLOADS[workload][0]
+    return M if workload != DEFAULT_WORKLOAD else min(M, CPU_SAMPLE_ROWS)
+
+
+def cpu_value(M_rows, N, K, bound, sec):
+    if bound == "tensor":
+        return 2.0 * M_rows * N * K / sec / 1e12, "TFLOP/s"
+    return (4 * M_rows * K + 4 * N * K + 4 * K + 4 * M_rows * N) / sec / 1e9, "GB/s"
+
+
+def cpu_sample_text(rows, M, N, K, threads):
+    return (f"{rows} of {M} rows x all N={N}, K={K}; fp32 torch CPU path of the reference (rms_norm then matmul), "
+            f"{threads} threads of {os.cpu_count()} cpus")
+
+
+def run_reference_arm(args, rank):
+    """The reference's own implementation of the path (its torch operator) on the host cores, same configuration,
+    metric and sample as the other arm's `cpu_baseline`; rank 0 only."""
+    if rank != 0:
+        return
+    M, N, K, bound, _ = WORKLOADS[args.workload]
+    rows = cpu_sample_rows(args.workload)
+    _, mean, n, threads = cpu_reference(M, N, K, rows, 0.0, steps=args.steps, warmup=args.warmup)
+    value, unit = cpu_value(rows, N, K, bound, mean)
+    sample = cpu_sample_text(rows, M, N, K, threads)
+    line = {
+        "impl": "reference", "metric": metric_name(bound), "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "eps": EPS, "gamma": True, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    if not args.no_extra and args.workload == DEFAULT_WORKLOAD:
+        m2, n2, k2, b2, _ = WORKLOADS["prefill_qkv_4096x6144x4096"]
+        med, _, n, threads = cpu_reference(m2, n2, k2, m2, 8.0)
+        v2, u2 = cpu_value(m2, n2, k2, b2, med)
+        line["extra"] = {"prefill_qkv_4096x6144x4096": {
+            "value": v2, "unit": u2, "ms_per_step": med * 1e3, "sample": cpu_sample_text(m2, m2, n2, k2, threads)}}
+    print(json.dumps(line), flush=True)
+
+
+class Runner:
+    """One workload on this rank's GPU: buffers, the step, timing windows, parity."""
+
+    def __init__(self, kb, name, dev, rank, world, variant="auto"):
+        self.kb, self.name, self.dev, self.rank, self.world, self.variant = kb, name, dev, rank, world, variant
+        self.M, self.N_total, self.K, self.bound, self.fp8 = WORKLOADS[name]
+        n0, n1 = shard_range(self.N_total, world, rank) if world > 1 else (0, self.N_total)
+        self.n0, self.n1, self.N = n0, n1, n1 - n0
+        self.step_bytes = algorithmic_bytes(self.M, self.N, self.K, self.fp8)
+        self.flops = 2.0 * self.M * self.N * self.K                    # this rank's share
+        self.flops_total = 2.0 * self.M * self.N_total * self.K
+        self.sets = max(2, -(-2 * L2_BYTES // self.step_bytes))        # rotate enough buffer sets to exceed 2x L2
+        self.bufs = make_buffers(self.M, self.N, self.K, dev, self.sets, seed=18 + 1000 * rank, fp8=self.fp8)
+        self.stream = torch.cuda.current_stream()
+        self.kernel = "e4m3 pair kernel"
+        if not self.fp8:
+            from kernel_benchmarking_b200 import _lib
+            v = _lib.load().rl_select_variant(self.M, self.N, self.K, 1, 1)
+            self.kernel = _lib.VARIANT_NAMES.get(v, str(v)) if variant == "auto" else str(variant)
+        # kernels launched per step: the pre-pass (row statistics / quantisation) and the GEMM, or one fused kernel
+        self.launches_per_step = 2 if (self.fp8 or "prestats" in self.kernel) else 1
+
+    def step(self, i):
+        x, g, W, y, wsc = self.bufs[i % self.sets]
+        self.kb.rmsnorm_linear(x, g, W, EPS, w_scale=wsc, out=y, variant="auto" if self.fp8 else self.variant)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def warm(self, warmup, spin_s=0.0):
+        for i in range(warmup):
+            self.step(i)
+        t0, i = time.perf_counter(), 0
+        while time.perf_counter() - t0 < spin_s:      # bring the part to its loaded state before the windows
+            self.step(i)
+            i += 1
+            if i % 8 == 0:
+                torch.cuda.synchronize()
+        self.barrier()
+
+    def windows(self, steps, n_windows):
+        """ms per step of each window: `steps` steps bracketed by a barrier + synchronize, CUDA events on the
+        launching stream, max over ranks."""
+        out = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(n_windows):
+            self.barrier()
+            e0.record(self.stream)
+            for i in range(steps):
+                self.step(i)
+            e1.record(self.stream)
+            self.barrier()
+            out.append(e0.elapsed_time(e1))
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor(out, device=self.dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out = t.tolist()
+        return [ms / steps for ms in out]
+
+    def value(self, ms_step):
+        if self.bound == "tensor":
+            return self.flops_total / (ms_step * 1e-3) / 1e12, "TFLOP/s"
+        # HBM-bound workloads are not sharded here: every rank streams its own W
+        return self.world * self.step_bytes / (ms_step * 1e-3) / 1e9, "GB/s"
+
+    def roofline(self, ms_step, peaks):
+        if self.bound == "tensor":
+            achieved, unit = self.flops / (ms_step * 1e-3) / 1e12, "TFLOP/s"
+            peak = peaks["bf16_tflops"] * (2 if self.fp8 else 1)
+            sustained = peaks["bf16_tflops_sustained"] * (2 if self.fp8 else 1)
+            src = f"of {peaks['source']} cuBLAS bf16 burst" + (" x 2 (no FP8 peak was measured)" if self.fp8 else "")
+        else:
+            achieved, unit = self.step_bytes / (ms_step * 1e-3) / 1e9, "GB/s"
+            peak, sustained = peaks["hbm_gbs"], None
+            src = f"of {peaks['source']} copy bandwidth"
+        r = {"bound": "tensor" if self.bound == "tensor" else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
+             "frac": achieved / peak, "peak_source": src,
+             "traffic": MEASURED_DRAM_BYTES.get((self.kernel, self.M, self.N, self.K)), "kernel": self.kernel,
+             "algorithmic_bytes": self.step_bytes, "algorithmic_flops": self.flops}
+        if sustained:
+            r["peak_sustained"] = sustained
+            r["frac_of_sustained"] = achieved / sustained
+        return r
+
+    def free(self):
+        self.bufs = None
+        torch.cuda.empty_cache()
+
+
+def run_extra(kb, name, dev, rank, world, steps, warmup, peaks, cpu_leg):
+    """One entry of the `extra` block."""
+    r = Runner(kb, name, dev, rank, world)
+    # short kernels: enough steps per window for a stable figure, and a short spin so clocks settle under load
+    est_steps = max(steps, 20) if r.bound == "tensor" else max(steps, 100)
+    sampler = ClockSampler(dev.index).start() if rank == 0 else None
+    r.warm(warmup, spin_s=0.15)
+    ms = r.windows(est_steps, 3)
+    clocks = sampler.stop() if sampler else None
+    kb.check_status()
+    err, tol = parity_check(r.bufs[(est_steps - 1) % r.sets], EPS, r.fp8)
+    med = statistics.median(ms)
+    value, unit = r.value(med)
+    entry = {"value": value, "unit": unit, "ms_per_step": med, "ms_per_step_windows": ms, "steps": est_steps,
+             "M": r.M, "N_per_gpu": r.N, "K": r.K, "scaling": "strong" if (world > 1 and r.bound == "tensor") else "replicas",
+             "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)" if r.fp8 else "bf16", "roofline": r.roofline(med, peaks),
+             "parity_max_rel_err": err, "parity_ok": err <= tol,
+             "clocks": None if clocks is None else {k: clocks[k] for k in ("sm_mhz", "sm_mhz_min", "reasons", "samples_under_load")}}
+    r.free()
+    if cpu_leg:
+        sec, _, n, threads = cpu_reference(r.M, r.N_total, r.K, r.M, 8.0)
+        cv, cu = cpu_value(r.M, r.N_total, r.K, r.bound, sec)
+        entry["cpu_baseline"] = {"value": cv, "unit": cu, "cores": threads, "kind": "port",
+                                 "sample": cpu_sample_text(r.M, r.M, r.N_total, r.K, threads) + f", median of {n} runs"}
+    return entry
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--variant", default="auto", help="kernel variant name (see kernel_benchmarking_b200._lib.VARIANTS)")
+    ap.add_argument("--no-extra", action="store_true", help="only the main workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--graph", action="store_true",
-                    help="M <= 64 workloads: time CUDA-graph replay instead of eager launches (measured: no faster, "
-                         "the call costs 11 us of host time against a 43 us kernel)")
     ap.add_argument("--profile", action="store_true",
-                    help="only warm-up + timed steps (no clock-sampling spin, no e2e, no CPU baseline): for ncu")
+                    help="only warm-up + timed steps of the workload (no clock sampling, e2e, extras or CPU legs): "
+                         "the command a profiler wraps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -240,195 +428,161 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
 
-    M, N, K, bound = WORKLOADS[args.workload]
-    strong = args.workload.startswith("strong_")
-    if strong:
-        from kernel_benchmarking_b200.sharding import shard_bounds
-        n0, n1 = shard_bounds(N, world, rank, multiple=256)
-        N = n1 - n0          # this rank's block of output channels
-    fp8 = "fp8w" in args.workload
-    step_bytes = algorithmic_bytes(M, N, K, fp8)
-    sets = max(2, -(-2 * L2_BYTES // step_bytes))   # rotate enough buffer sets to exceed 2x L2
-    bufs = make_buffers(M, N, K, dev, sets, seed=18 + rank, fp8=fp8)
-    stream = torch.cuda.current_stream()
-
-    def step(i):
-        x, g, W, y, _, wsc = bufs[i % sets]
-        kb.rmsnorm_linear(x, g, W, 1e-6, w_scale=wsc, out=y, variant=args.variant)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---------------- device-resident timing
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    # keep the GPU busy long enough for nvidia-smi to sample it under load, then time exactly K steps
-    t_spin = time.perf_counter()
-    i = 0
-    while not args.profile and time.perf_counter() - t_spin < 0.3:
-        step(i)
-        i += 1
-        if i % 16 == 0:
-            torch.cuda.synchronize()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # optional: replay a CUDA graph that holds one step per buffer set, as a serving loop would
-    use_graph = (bound == "hbm") and args.graph and not args.profile
-    eager_ms = None
-    if use_graph:
-        e0.record(stream)
-        for i in range(args.steps):
-            step(i)
-        e1.record(stream)
-        barrier()
-        eager_ms = e0.elapsed_time(e1) / args.steps
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            for i in range(sets):
-                step(i)                      # workspace for this stream exists before capture starts
-            side.synchronize()
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(sets):
-                    step(i)
-        torch.cuda.current_stream().wait_stream(side)
-        replays = max(1, args.steps // sets)
-        for _ in range(3):
-            graph.replay()
-        barrier()
-        e0.record(stream)
-        for _ in range(replays):
-            graph.replay()
-        e1.record(stream)
-        barrier()
-        timed_steps = replays * sets
-    else:
-        e0.record(stream)
-        for i in range(args.steps):
-            step(i)
-        e1.record(stream)
-        barrier()
-        timed_steps = args.steps
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = e0.elapsed_time(e1)
-    kb.check_status()
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / timed_steps
-    flops = 2.0 * M * N * K
-    if bound == "tensor":
-        value, unit = world * flops / (ms_step * 1e-3) / 1e12, "TFLOP/s"
-    else:
-        value, unit = world * step_bytes / (ms_step * 1e-3) / 1e9, "GB/s"
+    run = Runner(kb, args.workload, dev, rank, world, variant=args.variant)
+    M, N, K = run.M, run.N, run.K
 
     if args.profile:
+        run.warm(args.warmup)
+        ms = run.windows(args.steps, 1)[0]
         if rank == 0:
-            print(json.dumps({"profile_run": True, "workload": args.workload, "ms_per_step": ms_step, "value": value,
-                              "unit": unit}), flush=True)
+            v, u = run.value(ms)
+            print(json.dumps({"profile_run": True, "workload": args.workload, "kernel": run.kernel, "ms_per_step": ms,
+                              "value": v, "unit": u}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
 
+    # ---------------- device-resident timing: 5 windows of --steps steps, clocks sampled throughout
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    run.warm(args.warmup, spin_s=0.3)
+    win_ms = run.windows(args.steps, WINDOWS)
+    clocks = sampler.stop() if sampler else None
+    kb.check_status()
+    ms_step = statistics.median(win_ms)
+    value, unit = run.value(ms_step)
+
+    # ---------------- parity of this rank's shard, outside the timed region
+    err, tol = parity_check(run.bufs[(args.steps - 1) % run.sets], EPS, run.fp8)
+    parity = torch.tensor([err], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(parity, op=dist.ReduceOp.MAX)
+    parity_err = float(parity.item())
+
     # ---------------- end to end: host buffers, copies inside the timed region
-    # Through the package's host-buffer front end: every step copies its x from pinned host memory and
-    # its y back to pinned host memory; the three stages of consecutive steps overlap on three streams.
-    x_host = [b[4].pin_memory() for b in bufs[:2]]
+    # Through the package's host-buffer front end: every step copies its x from pinned host memory and its y
+    # (this rank's columns) back to pinned host memory; the three stages of consecutive steps overlap on three streams.
+    x_host = [run.bufs[i][0].cpu().pin_memory() for i in range(2)]
     y_host = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    host_op = kb.HostRMSNormLinear(bufs[0][1], bufs[0][2], 1e-6, w_scale=bufs[0][5], max_tokens=M, depth=2,
+    host_op = kb.HostRMSNormLinear(run.bufs[0][1], run.bufs[0][2], EPS, w_scale=run.bufs[0][4], max_tokens=M, depth=2,
                                    variant=args.variant)
-    e2e_steps = max(3, min(args.steps, 20))
-    for i in range(3):
+    e2e_steps = max(3, min(args.steps, 8))
+    for i in range(2):
         host_op.submit(x_host[i % 2], y_host[i % 2])
     host_op.wait()
-    barrier()
+    run.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(host_op.s_in)
     for i in range(e2e_steps):
         host_op.submit(x_host[i % 2], y_host[i % 2])
     e1.record(host_op.s_out)
     host_op.wait()
-    barrier()
+    run.barrier()
     e2e_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_ms /= e2e_steps
-    e2e_value = (world * flops / (e2e_ms * 1e-3) / 1e12) if bound == "tensor" else (world * step_bytes / (e2e_ms * 1e-3) / 1e9)
+    e2e_value = run.value(e2e_ms)[0]
+    # the copied-back result is the kernel's: same bits as the device-resident run on the same inputs
+    e2e_same = bool(torch.equal(y_host[(e2e_steps - 1) % 2], _rerun(kb, run, x_host[(e2e_steps - 1) % 2], args.variant)))
+    del host_op, y_host, x_host
+    torch.cuda.empty_cache()
 
     # ---------------- optional assembled-y all-gather, timed on its own
-    gather_ms = None
-    if world > 1:
+    gather = None
+    if world > 1 and run.bound == "tensor" and not run.fp8:
         from kernel_benchmarking_b200.sharding import ColumnParallelRMSNormLinear
-        op = ColumnParallelRMSNormLinear(bufs[0][2], bufs[0][1], 1e-6, N * world)
-        y_local = bufs[0][3]
-        for _ in range(2):
-            op.gather(y_local)
-        barrier()
-        e0.record(stream)
-        for _ in range(5):
-            op.gather(y_local)
-        e1.record(stream)
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gather_ms = float(t.item())
+        x, g, W, _, _ = run.bufs[0]
+        op = ColumnParallelRMSNormLinear(W, g, EPS, run.N_total, multiple=256)
+        y_local = op.forward(x)                      # lands in this rank's block of the gather buffer
+        res = {}
+        for layout in ("blocked", "row_major"):
+            for _ in range(2):
+                op.gather(y_local, layout=layout)
+            run.barrier()
+            e0.record(run.stream)
+            for _ in range(5):
+                op.gather(y_local, layout=layout)
+            e1.record(run.stream)
+            run.barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[layout] = float(t.item())
+        recv = 2.0 * M * (run.N_total - N)           # bytes this rank receives
+        gather = {"ms_blocked": res["blocked"], "ms_row_major": res["row_major"],
+                  "received_gb_per_s_blocked": recv / (res["blocked"] * 1e-3) / 1e9,
+                  "note": "NCCL all-gather of y [M, N] in place into a [G, M, N/G] buffer the kernel wrote its block "
+                          "into (blocked); row_major adds one strided copy of the whole tensor"}
+        del op, y_local
+        torch.cuda.empty_cache()
 
+    line = None
     if rank == 0:
-        peaks = measured_peaks()
-        per_gpu_ms = ms_step
-        if bound == "tensor":
-            achieved, peak, r_unit = flops / (per_gpu_ms * 1e-3) / 1e12, peaks["bf16_tflops"] * (2 if fp8 else 1), "TFLOP/s"
-        else:
-            achieved, peak, r_unit = step_bytes / (per_gpu_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
         line = {
-            "metric": metric_name(bound), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
-            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)" if fp8 else "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "M": M, "N_per_gpu": N, "K": K, "eps": 1e-6, "gamma": True,
-                       "sharding": f"column-parallel x{world}, x replicated, no collective",
-                       "l2": f"inputs larger than L2: {sets} rotating buffer sets of {step_bytes / 1e6:.0f} MB",
-                       "variant": args.variant,
-                       "launch": "CUDA graph replay" if use_graph else "eager"},
+            "metric": metric_name(run.bound), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if run.bound == "tensor" else "replicas",
+            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)" if run.fp8 else "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "M": M, "N_total": run.N_total, "N_per_gpu": N, "K": K, "eps": EPS,
+                       "gamma": True,
+                       "sharding": f"W split along N over {world} rank(s), x replicated, no collective on the data path",
+                       "l2": f"inputs larger than L2: {run.sets} rotating buffer sets of {run.step_bytes / 1e6:.0f} MB",
+                       "variant": args.variant, "kernel": run.kernel, "windows": WINDOWS,
+                       "timing": f"median of {WINDOWS} windows of {args.steps} steps, each bracketed by barrier + "
+                                 "synchronize, CUDA events, max over ranks"},
+            "ms_per_step_windows": win_ms,
+            "ms_per_step_spread": (max(win_ms) - min(win_ms)) / ms_step,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N,
-                    "ms_per_step": e2e_ms, "note": "HostRMSNormLinear: x from pinned host memory and y back to pinned host "
-                    "memory every step, copy-in / kernel / copy-out of consecutive steps overlapped on three streams; "
-                    "W and gamma are weights, resident on the device"},
-            # M > 128 and the FP8 path launch two kernels per step (row statistics / quantisation, then the GEMM)
-            "gpu_launches": timed_steps * world * (2 if (fp8 or M > 128) else 1),
-            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peaks['source']}" + (" bf16 x 2 (no FP8 peak was measured)" if fp8 else ""),
-                         "algorithmic_bytes": step_bytes, "algorithmic_flops": flops},
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "same_bits_as_device_run": e2e_same,
+                    "note": "HostRMSNormLinear: x from pinned host memory and this rank's y back to pinned host memory "
+                            "every step (bytes are per rank), copy-in / kernel / copy-out of consecutive steps "
+                            "overlapped on three streams; W and gamma are weights, resident on the device"},
+            "gpu_launches": WINDOWS * args.steps * world * run.launches_per_step,
+            "roofline": run.roofline(ms_step, peaks),
+            "parity_checked": True, "parity_max_rel_err": parity_err, "parity_tolerance": tol,
+            "parity_ok": parity_err <= tol,
+            "parity_note": "every rank: 64 seeded rows of its y[:, n0:n1] against rms_norm + matmul in fp32 on its GPU",
         }
-        if gather_ms is not None:
-            line["gather_ms"] = gather_ms
-        if eager_ms is not None:
-            line["eager_ms_per_step"] = eager_ms
-            line["steps"] = timed_steps
+        if gather is not None:
+            line["gather_ms"] = gather["ms_blocked"]
+            line["gather"] = gather
+    run.free()
+
+    # ---------------- further workloads
+    if not args.no_extra and args.workload == DEFAULT_WORKLOAD:
+        extra = {}
+        for name in (EXTRA_1GPU if world == 1 else EXTRA_MULTI):
+            cpu_leg = (world == 1 and name == "prefill_qkv_4096x6144x4096" and not args.no_cpu_baseline)
+            extra[name] = run_extra(kb, name, dev, rank, world, args.steps, args.warmup, peaks, cpu_leg and rank == 0)
+        if rank == 0:
+            b, f = extra.get("bf16_8192x14336x4096"), extra.get("fp8w_8192x14336x4096")
+            if b and f:
+                extra["fp8_over_bf16"] = f["value"] / b["value"]
+            line["extra"] = extra
+
+    if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            rows, med, reps = cpu_reference_time(M, N, K)
-            cores = torch.get_num_threads()
-            if bound == "tensor":
-                cv, cu = 2.0 * rows * N * K / med / 1e12, "TFLOP/s"
-            else:
-                cv, cu = (4 * rows * K + 4 * N * K + 4 * K + 4 * rows * N) / med / 1e9, "GB/s"
-            line["cpu_baseline"] = {"value": cv, "unit": cu, "cores": cores, "kind": "port",
-                                    "sample": f"{rows} of {M} rows x all N, K; fp32 torch CPU path of the reference "
-                                              f"(rms_norm then matmul), median of {reps} runs, {cores} threads of "
-                                              f"{os.cpu_count()} cpus"}
+            rows = cpu_sample_rows(args.workload)
+            sec, _, n, threads = cpu_reference(run.M, run.N_total, run.K, rows, 12.0)
+            cv, cu = cpu_value(rows, run.N_total, run.K, run.bound, sec)
+            line["cpu_baseline"] = {"value": cv, "unit": cu, "cores": threads, "kind": "port",
+                                    "sample": cpu_sample_text(rows, run.M, run.N_total, run.K, threads) + f", median of {n} runs"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def _rerun(kb, run, x_host, variant):
+    """The device-resident result for one host batch (same weights as the end-to-end front end uses)."""
+    _, g, W, _, wsc = run.bufs[0]
+    y = kb.rmsnorm_linear(x_host.to(run.dev), g, W, EPS, w_scale=wsc, variant="auto" if run.fp8 else variant)
+    torch.cuda.synchronize()
+    return y.cpu()
 
 
 if __name__ == "__main__":

@@ -249,6 +249,9 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
 #define RL_GROUP_BUDGET_MB 40
 #endif
 int pick_group_m(int m_tiles, long long row_tile_bytes) {
+#ifdef RL_GROUP_M_FIXED
+  return RL_GROUP_M_FIXED;
+#endif
   long long g = ((long long)RL_GROUP_BUDGET_MB << 20) / (row_tile_bytes > 0 ? row_tile_bytes : 1);
   if (g < 4) g = 4;
   if (g > m_tiles) g = m_tiles;

@@ -29,6 +29,13 @@ RMSNORM_LINEAR_SHAPES: Tuple[Tuple[int, int, int], ...] = (
     (1024, 14336, 4096), (1024, 28672, 8192), (1024, 16384, 2048),
     (4096, 1024, 4096), (4096, 1024, 8192), (4096, 1536, 7168), (4096, 1024, 16384),
 )
+# The reference's second shape list (res/cdsl_rmsnorm_shapes_m128n256.txt:1-7); the first three are also in the
+# table above.  Its committed H100 timings for these shapes are in res/c2_kernels/results.json.
+EXTRA_SHAPES: Tuple[Tuple[int, int, int], ...] = (
+    (2048, 2048, 2048), (4096, 4096, 4096), (1024, 16384, 2048),
+    (1024, 32768, 4096), (1024, 4096, 16384), (8192, 1024, 2048), (8192, 2048, 4096),
+)
+B200_DENSE_BF16_TFLOPS = 2250.0   # nominal dense bf16 tensor peak, the denominator of `pct_peak` in the metadata column
 REFERENCE_EPS = 1e-5   # python/workload_shapes.py:42-47
 CSV_FIELDS = ("label", "m", "n", "k", "ms_median", "ms_mean", "ms_std", "max_abs", "max_rel", "rmse",
               "baseline_speedup", "metadata", "autotune_seconds")
@@ -123,6 +130,20 @@ class ExperimentRow:
         self.ms_median = statistics.median(times)
         self.ms_mean = statistics.fmean(times)
         self.ms_std = statistics.pstdev(times)
+        self.metadata = throughput_metadata(self.m, self.n, self.k, self.ms_median)
+
+
+def throughput_metadata(m, n, k, ms_median, n_gpus: int = 1, elem_bytes: int = 2) -> Optional[str]:
+    """The free-form `metadata` column (profile_utils.py:87): derived throughput figures, `;`-separated so the
+    row stays one CSV record.  tflops = 2 m n k / time; pct_peak against the nominal dense bf16 tensor peak;
+    gbps = bytes of x, W and y over time."""
+    if not (m and n and k and ms_median):
+        return None
+    sec = ms_median * 1e-3
+    tflops = 2.0 * m * n * k / sec / 1e12
+    gbps = elem_bytes * (m * k + n * k + m * n) / sec / 1e9
+    return (f"tflops={tflops:.1f};pct_peak={100.0 * tflops / (B200_DENSE_BF16_TFLOPS * n_gpus):.1f};"
+            f"gbps={gbps:.0f};n_gpus={n_gpus}")
 
 
 class ProfilingJob:
@@ -167,13 +188,17 @@ def write_rows(rows, path: Optional[str] = None) -> None:
         f.write("".join(r.csv() + "\n" for r in rows))
 
 
-def rmsnorm_linear_job(config: int, seed: int = 18) -> ProfilingJob:
-    """The job of demo/new_profiling/rmsnorm_linear_new.py for shape `config`, with the kernels that exist here:
-    `b200` (this library), `torch` (eager rms_norm + matmul, the baseline) and `max` (plain matmul)."""
+def rmsnorm_linear_job(config: int, seed: int = 18, shapes: Sequence[Tuple[int, int, int]] = RMSNORM_LINEAR_SHAPES,
+                       shape: Optional[Tuple[int, int, int]] = None) -> ProfilingJob:
+    """The job of demo/new_profiling/rmsnorm_linear_new.py for shape `config` of `shapes` (or an explicit `shape`,
+    labelled with `config`), with the kernels that exist here: `b200` (this library), `torch` (eager rms_norm +
+    matmul, the baseline), `max` (plain matmul) and `max_b200` (this library's plain GEMM)."""
     from .ops import gemm_nt, rmsnorm_linear
-    if not 0 <= config < len(RMSNORM_LINEAR_SHAPES):
-        raise IndexError(f"config must be in [0, {len(RMSNORM_LINEAR_SHAPES)})")
-    m, n, k = RMSNORM_LINEAR_SHAPES[config]
+    if shape is None:
+        if not 0 <= config < len(shapes):
+            raise IndexError(f"config must be in [0, {len(shapes)})")
+        shape = shapes[config]
+    m, n, k = shape
     g = torch.Generator().manual_seed(seed)
     a64 = normal_bernoulli((m, k), generator=g)
     b64 = normal_bernoulli((n, k), generator=g)
@@ -224,20 +249,112 @@ def lora_job(config: int, seed: int = 18) -> ProfilingJob:
                         ref_by_kernel={"max": ref_gemm, "max_b200": ref_gemm})
 
 
-def main(argv=None) -> None:
-    """`python -m kernel_benchmarking_b200.harness CONFIG [--workload rmsnorm_linear|lora] [--ncu] [--csv FILE]` - the
-    new-style CLI of the reference (profile_utils.py:444-456); `--header` prints the CSV header (demo/gen_header.py)."""
-    ap = argparse.ArgumentParser(description=main.__doc__)
-    ap.add_argument("config", type=int, nargs="?", default=0)
-    ap.add_argument("--workload", default="rmsnorm_linear", choices=["rmsnorm_linear", "lora"])
+def parse_new_style(argv=None) -> argparse.Namespace:
+    """`CONFIG [--ncu] [--csv FILE]` (profile_utils.py:444-456) plus this harness's additions."""
+    ap = argparse.ArgumentParser(description="Profiling program for the RMSNorm -> Linear workload (config = row of the shape table)")
+    ap.add_argument("config", type=int, nargs="?", default=0, help="the config number")
     ap.add_argument("--ncu", action="store_true")
-    ap.add_argument("--csv", default=None)
-    ap.add_argument("--header", action="store_true")
-    ns = ap.parse_args(argv)
+    ap.add_argument("--csv", default=None, help="append the results to csv file instead of stdout")
+    ap.add_argument("--workload", default="rmsnorm_linear", choices=["rmsnorm_linear", "lora"])
+    ap.add_argument("--shapes", default="gemm", choices=["gemm", "extra"],
+                    help="gemm: python/workload_shapes.py GEMM_SHAPES; extra: res/cdsl_rmsnorm_shapes_m128n256.txt")
+    ap.add_argument("--header", action="store_true", help="print the CSV header (demo/gen_header.py) and exit")
+    ap.add_argument("--all", action="store_true",
+                    help="every config of the shape table, one process each, into --csv (run_scripts/profile_rmsnorm_linear.sh)")
+    return ap.parse_args(argv)
+
+
+def parse_old_style(argv) -> argparse.Namespace:
+    """`m n k [--to_csv]` (`get_args`, profile_utils.py:219-234)."""
+    ap = argparse.ArgumentParser(description="Profiling Program For Gemm-Based Kernel")
+    ap.add_argument("m", type=int)
+    ap.add_argument("n", type=int)
+    ap.add_argument("k", type=int)
+    ap.add_argument("--to_csv", action="store_true")   # doubles as the reference's print flag
+    return ap.parse_args(argv)
+
+
+def is_old_style(argv: Sequence[str]) -> bool:
+    """Three leading integers select the old entry (demo/rmsnorm_linear.py), one (or none) the new one."""
+    lead = []
+    for a in argv:
+        if a.startswith("-"):
+            break
+        lead.append(a)
+    return len(lead) == 3 and all(x.lstrip("+").isdigit() for x in lead)
+
+
+def run_old_style(ns: argparse.Namespace, out=print) -> list:
+    """The old entry point (demo/rmsnorm_linear.py:40-104) for one explicit shape: rows for `torch`, `b200` and
+    `max`; with --to_csv they are printed as CSV records, otherwise as the header, the value lists, the speed-up
+    of the fused kernel over the baseline and the "max attainable speedup" line (baseline time over plain GEMM
+    time, with the norm's own time beside it)."""
+    job = rmsnorm_linear_job(0, shape=(ns.m, ns.n, ns.k))
+    job.workload, job.config = "rmsnorm_linear", f"{ns.m}x{ns.n}x{ns.k}"
+    rows = job.run()
+    by = {r.label.split(":")[-1]: r for r in rows}
+    order = [by["torch"], by["b200"], by["max"], by["max_b200"]]
+    if ns.to_csv:
+        for r in order:
+            out(r.csv())
+        return rows
+    out(ExperimentRow.header())
+    for r in order[:3]:
+        out([getattr(r, f) for f in CSV_FIELDS])
+    out(by["torch"].ms_median / by["b200"].ms_median)
+    a = job.args[0]
+    rmsnorm_ms = statistics.median(bench_with_l2_flush(
+        lambda: torch.nn.functional.rms_norm(a, (a.shape[1],), eps=REFERENCE_EPS), min_reps=30))
+    gemm_ms = by["max"].ms_median
+    out(f"rmsnorm_ms={rmsnorm_ms}, gemm_ms={gemm_ms}. Max speedup = {by['torch'].ms_median / gemm_ms}")
+    return rows
+
+
+def run_all(csv_path: str, shapes: str = "gemm", workload: str = "rmsnorm_linear", pause_s: float = 3.0,
+            runner=None) -> int:
+    """The batch driver (run_scripts/profile_rmsnorm_linear.sh:6-17): write the header into the CSV (overwriting
+    it), then one process per config appending its rows, a pause between them.  The reference's loop runs one
+    index past its 10-row table; this one stops at the last row."""
+    import os
+    import subprocess
+    import sys
+    d = os.path.dirname(csv_path)
+    if d:
+        os.makedirs(d, exist_ok=True)
+    with open(csv_path, "w") as f:
+        f.write(ExperimentRow.header() + "\n")
+    n = len(EXTRA_SHAPES if shapes == "extra" else RMSNORM_LINEAR_SHAPES)
+    failed = 0
+    for i in range(n):
+        cmd = [sys.executable, "-m", "kernel_benchmarking_b200.harness", str(i), "--csv", csv_path, "--shapes", shapes,
+               "--workload", workload]
+        rc = runner(cmd) if runner is not None else subprocess.run(cmd).returncode
+        failed += 1 if rc else 0
+        if runner is None and i + 1 < n:
+            time.sleep(pause_s)
+    return failed
+
+
+def main(argv=None) -> None:
+    """New style: `python -m kernel_benchmarking_b200.harness CONFIG [--workload rmsnorm_linear|lora] [--shapes gemm|extra]
+    [--ncu] [--csv FILE] [--all] [--header]`; old style: `python -m kernel_benchmarking_b200.harness M N K [--to_csv]`."""
+    import sys
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if is_old_style(argv):
+        run_old_style(parse_old_style(argv))
+        return
+    ns = parse_new_style(argv)
     if ns.header:
         print(ExperimentRow.header())
         return
-    job = lora_job(ns.config) if ns.workload == "lora" else rmsnorm_linear_job(ns.config)
+    if ns.all:
+        csv_path = ns.csv or time.strftime("results/rmsnorm_linear_%Y%m%d_%H%M%S.csv")
+        print(f"writing csv to {csv_path}")
+        raise SystemExit(1 if run_all(csv_path, ns.shapes, ns.workload) else 0)
+    shapes = EXTRA_SHAPES if ns.shapes == "extra" else RMSNORM_LINEAR_SHAPES
+    job = lora_job(ns.config) if ns.workload == "lora" else rmsnorm_linear_job(ns.config, shapes=shapes)
+    if ns.shapes == "extra":
+        job.workload = "rmsnorm_linear_extra"
     write_rows(job.run(ncu=ns.ncu), ns.csv)
 
 

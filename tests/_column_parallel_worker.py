@@ -8,7 +8,7 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 import kernel_benchmarking_b200 as kb  # noqa: E402
-from kernel_benchmarking_b200.sharding import ColumnParallelRMSNormLinear, shard_rows  # noqa: E402
+from kernel_benchmarking_b200.sharding import ColumnParallelRMSNormLinear, shard_bounds, shard_rows  # noqa: E402
 from oracle import rmsnorm_linear_oracle as orc  # noqa: E402
 
 
@@ -22,13 +22,19 @@ def main():
     for (M, N, K) in [(300, 1024, 512), (16, 2048, 1024), (1000, 1032, 256)]:
         x, gm, W = orc.make_inputs(M, N, K, seed=7)           # identical on every rank
         op = ColumnParallelRMSNormLinear(shard_rows(W, world, rank).contiguous().to(dev), gm.to(dev), 1e-6, N)
-        y_local = op.forward(x.to(dev))
+        y_local = op.forward(x.to(dev))               # written straight into this rank's block of the gather buffer
         y = op.gather(y_local)
         torch.cuda.synchronize()
         kb.check_status()
         ref = orc.reference_fp32(x, gm, W, 1e-6)
         err = orc.rel_max_err(y.cpu(), ref)
         ok = ok and y.shape == (M, N) and err <= 1e-2
+        yb = op.gather(y_local, layout="blocked")     # [M, G, Nb]: no copy behind the all-gather
+        torch.cuda.synchronize()
+        for r in range(world):
+            a, b = shard_bounds(N, world, r)
+            ok = ok and torch.equal(yb[:, r, : b - a], y[:, a:b])
+        ok = ok and y_local.data_ptr() == yb[:, rank].data_ptr()
         # the single-GPU kernel on the whole weight gives the same columns: to one bf16 ulp (2^-7), since tiles of
         # the last round may be summed in k-slices and which tiles those are depends on the shard's tile count
         if M > 64 and rank == 0:

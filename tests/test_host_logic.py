@@ -72,6 +72,13 @@ def _rank_main(rank, world, port, N, q):
         ok_local = torch.allclose(y_local, full[:, n0:n1], rtol=1e-5, atol=1e-6)
         y = op.gather(y_local)
         ok_full = y.shape == full.shape and torch.allclose(y, full, rtol=1e-5, atol=1e-6)
+        # the blocked layout is the gather buffer as it lies: element [m, r, j] is y[m, n0_r + j]
+        yb = op.gather(y_local, layout="blocked")
+        ok_full = ok_full and yb.shape[:2] == (M, world)
+        for r in range(world):
+            a, b = shard_bounds(N, world, r)
+            ok_full = ok_full and torch.allclose(yb[:, r, : b - a], full[:, a:b], rtol=1e-5, atol=1e-6)
+        ok_full = ok_full and op.gather(y_local).data_ptr() == y.data_ptr()     # buffers are kept between calls
         # e4m3 weights: the rank's slice of the per-channel scales travels with its rows of W
         Wq, wsc = orc.quantize_weight_e4m3(W)
 
@@ -138,3 +145,36 @@ def test_harness_metrics_and_distribution():
     g = torch.Generator().manual_seed(1)
     t = harness.normal_bernoulli((2000, 500), generator=g)
     assert 0.9 < float(t.std()) < 1.2 and float(t.abs().max()) > 8.0
+
+
+def test_harness_command_lines(tmp_path):
+    """Both of the reference's entry styles parse, the batch driver writes the header and visits every config once."""
+    from kernel_benchmarking_b200 import harness
+    assert harness.is_old_style(["4096", "1024", "4096"]) and harness.is_old_style(["2048", "2048", "2048", "--to_csv"])
+    assert not harness.is_old_style(["3"]) and not harness.is_old_style(["3", "--csv", "x.csv"]) and not harness.is_old_style([])
+    ns = harness.parse_old_style(["4096", "1536", "7168", "--to_csv"])
+    assert (ns.m, ns.n, ns.k, ns.to_csv) == (4096, 1536, 7168, True)
+    ns = harness.parse_new_style(["7", "--csv", "r.csv", "--ncu"])
+    assert (ns.config, ns.csv, ns.ncu, ns.workload, ns.shapes) == (7, "r.csv", True, "rmsnorm_linear", "gemm")
+    # the four shapes the second list adds to the table
+    assert set(harness.EXTRA_SHAPES) - set(harness.RMSNORM_LINEAR_SHAPES) == {
+        (1024, 32768, 4096), (1024, 4096, 16384), (8192, 1024, 2048), (8192, 2048, 4096)}
+    seen = []
+    csv = tmp_path / "res" / "all.csv"
+    assert harness.run_all(str(csv), runner=lambda cmd: seen.append(cmd) or 0) == 0
+    assert csv.read_text() == harness.ExperimentRow.header() + "\n"
+    assert [c[3] for c in seen] == [str(i) for i in range(10)]           # stops at index 9
+    assert all(c[1:3] == ["-m", "kernel_benchmarking_b200.harness"] and str(csv) in c for c in seen)
+    seen.clear()
+    harness.run_all(str(csv), shapes="extra", runner=lambda cmd: seen.append(cmd) or 0)
+    assert len(seen) == 7 and all("extra" in c for c in seen)
+
+
+def test_harness_metadata_column():
+    from kernel_benchmarking_b200 import harness
+    md = harness.throughput_metadata(4096, 4096, 4096, 0.1)
+    assert md == "tflops=1374.4;pct_peak=61.1;gbps=1007;n_gpus=1"
+    assert "," not in md                       # stays one CSV field
+    assert harness.throughput_metadata(4096, 4096, 4096, None) is None
+    row = harness.ExperimentRow("rmsnorm_linear:1:b200", 4096, 4096, 4096, ms_median=0.1, metadata=md)
+    assert row.csv().split(",")[11] == md
