@@ -381,13 +381,16 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   p.KB = (K + 63) / 64;
   const long long units = (long long)p.n_tiles * p.KB;
   if (units > 0x7fffffffLL) return RL_ERR_BAD_SHAPE;
-  p.units_total = (int)units;
   p.status = reinterpret_cast<int*>(ws);
   p.counters = reinterpret_cast<int*>(ws + wl.counters_off);
   p.ssq_partials = reinterpret_cast<float*>(ws + wl.ssq_off);
   p.partials = reinterpret_cast<float*>(ws + wl.partials_off);
   int grid = sms < RL_MAX_CTAS ? sms : RL_MAX_CTAS;
   if (units < grid) grid = (int)units;
+  // every CTA owns floor(tiles / grid) tiles whole; the k-loops of the other tiles are shared out evenly
+  p.whole_per_cta = p.n_tiles / grid;
+  p.sk_tiles = p.n_tiles - p.whole_per_cta * grid;
+  p.units_total = p.sk_tiles * p.KB;
   cudaError_t e = set_smem_once(decode_kernel<Cfg>, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_err(e);
   // Programmatic stream serialisation: this grid's prologue (barrier setup, tensor-memory allocation,

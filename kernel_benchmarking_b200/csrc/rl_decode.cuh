@@ -2,15 +2,19 @@
 //
 // Operands are swapped so that the 128-wide UMMA M dimension runs over output
 // channels: A = W tile [128 channels x 64], B = (x*gamma) tile [MPAD tokens x 64],
-// D[channel, token] in TMEM.  The (channel-tile, k-block) units are dealt out
-// stream-K style: CTA c of G streams one contiguous run of units, so every SM
-// pulls the same share of W through a deep TMA ring.  A channel tile whose
-// k-range is split over several CTAs is finished by the last CTA to arrive:
-// every contributor writes its fp32 partial tile and its partial sum of
-// squares to the workspace and bumps the tile's counter; whoever sees the final
-// count adds the partials in contributor order (so the result does not depend
-// on arrival order), applies 1/rms per token and stores y.  No CTA ever waits
-// for another.  Counters are left at zero for the next launch.
+// D[channel, token] in TMEM.  Work is counted in (channel-tile, k-block) units and
+// every SM pulls the same share of W through a deep TMA ring.  With T channel
+// tiles on G CTAs each CTA owns floor(T / G) tiles whole; the k-loops of the
+// remaining T mod G tiles are dealt out stream-K style, CTA c taking one contiguous
+// run of their units.  A CTA does its share of the split tiles first and its own
+// tiles last, so the exchange between CTAs happens early, hidden behind the rest
+// of the stream, and the kernel ends on an epilogue that needs nobody else.
+// A split tile is finished by the last CTA to arrive: every contributor writes
+// its fp32 partial tile and its partial sum of squares to the workspace and bumps
+// the tile's counter; whoever sees the final count adds the partials in contributor
+// order (so the result does not depend on arrival order), applies 1/rms per token
+// and stores y.  No CTA ever waits for another.  Counters are left at zero for
+// the next launch.
 //
 // Warp roles: 0 TMA producer, 1 UMMA issuer, 2-5 transform (sum of squares via
 // warp shuffles + gamma fold in shared memory), 6-9 epilogue.
@@ -25,7 +29,10 @@ struct DecodeParams {
   const __nv_bfloat16* gamma;  // [K] or nullptr
   __nv_bfloat16* y;
   long long ldy;
-  int n_tiles, KB, units_total;
+  int n_tiles, KB;
+  int sk_tiles;      // tiles [0, sk_tiles) are split along K over all CTAs (stream-K); the rest are owned whole
+  int units_total;   // sk_tiles * KB: the units of the split part
+  int whole_per_cta; // tiles sk_tiles + cta + i * grid, i < whole_per_cta, belong to CTA `cta`
   int* status;
   int* counters;        // [n_tiles], zero between launches
   float* partials;      // [grid][2][MPAD][128]
@@ -69,19 +76,29 @@ __host__ __device__ __forceinline__ int sk_cta_of_unit(int u, int total, int G) 
   return (u < cut) ? u / (q + 1) : rem + (u - cut) / q;
 }
 
-// A CTA's contiguous run of units, cut at channel-tile boundaries, gives its segments.  They are
-// processed rotated by one - last segment first - so that the partial tiles at both ends of the run
-// (the ones shared with other CTAs) are done early and their cross-CTA fix-up hides
-// behind the whole tiles in the middle; the kernel then ends on a tile it owns alone.
+// A CTA's work as a list of segments (a tile's k-range, or part of it).  First its contiguous run of the
+// split part's units, cut at channel-tile boundaries and rotated by one - last piece first - so that the
+// pieces at both ends of the run (the ones shared with other CTAs) are done early; then the tiles it owns whole.
 struct DecodeSegments {
-  int u_begin, u_end, KB, first_tile, nseg;
-  __device__ __forceinline__ DecodeSegments(int b, int e, int kb) : u_begin(b), u_end(e), KB(kb) {
+  int u_begin, u_end, KB, first_tile, nseg_sk, nseg, whole0, whole_stride;
+  __device__ __forceinline__ DecodeSegments(int b, int e, int kb, int whole_first, int whole_count, int stride)
+      : u_begin(b), u_end(e), KB(kb), whole0(whole_first), whole_stride(stride) {
     first_tile = b / kb;
-    nseg = (e - 1) / kb - first_tile + 1;
+    nseg_sk = (e > b) ? (e - 1) / kb - first_tile + 1 : 0;
+    nseg = nseg_sk + whole_count;
   }
-  // i-th segment in processing order -> natural index, channel tile, first k-block, unit count
+  __device__ __forceinline__ int units() const { return (u_end - u_begin) + (nseg - nseg_sk) * KB; }
+  // i-th segment in processing order -> natural index within the split run (-1 for an owned tile), channel
+  // tile, first k-block, unit count
   __device__ __forceinline__ void get(int i, int& nat, int& tile, int& kb0, int& n_units) const {
-    nat = (nseg >= 2) ? (i == 0 ? nseg - 1 : i - 1) : i;
+    if (i >= nseg_sk) {
+      nat = -1;
+      tile = whole0 + (i - nseg_sk) * whole_stride;
+      kb0 = 0;
+      n_units = KB;
+      return;
+    }
+    nat = (nseg_sk >= 2) ? (i == 0 ? nseg_sk - 1 : i - 1) : i;
     tile = first_tile + nat;
     const int s = max(u_begin, tile * KB), e = min(u_end, (tile + 1) * KB);
     kb0 = s - tile * KB;
@@ -117,7 +134,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   const int u_begin = sk_begin(cta, p.units_total, G);
   const int u_end = sk_begin(cta + 1, p.units_total, G);
   const bool has_gamma = (p.gamma != nullptr);
-  const DecodeSegments segs(u_begin, u_end, KB);
+  const DecodeSegments segs(u_begin, u_end, KB, p.sk_tiles + cta, p.whole_per_cta, G);
 
   // one unit's loads: W tile (streamed once: evict-first), x tile (re-read by every CTA: evict-last), gamma slice
   auto issue_unit = [&](int s, int tile, int kb, uint64_t pol_w, uint64_t pol_x) {
@@ -128,7 +145,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
     if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
   };
-  const int n_pre = min(STAGES, u_end - u_begin);  // units whose loads go out before the CTA-wide sync
+  const int n_pre = min(STAGES, segs.units());  // units whose loads go out before the CTA-wide sync
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {

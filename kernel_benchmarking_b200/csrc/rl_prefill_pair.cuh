@@ -29,14 +29,9 @@
 
 namespace rl {
 
-#ifndef RL_PAIR_PREFETCH
-#define RL_PAIR_PREFETCH 0
-#endif
-
 template <int BN_, int NACC_, int STAGES_, int ASLOTS_, int TG_, int AMODE_, bool PRESTATS_ = false, bool SWIGLU_ = false,
           bool FP8_ = false>
 struct PairCfg {
-  static constexpr int PREFETCH = RL_PAIR_PREFETCH;  // k-blocks the producer's L2 prefetch runs ahead of its loads (0 = off)
   static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_, ASLOTS = ASLOTS_, TG = TG_, AMODE = AMODE_;
   // PRESTATS: 1/rms per token comes from rowstats_kernel; the transform warps only fold gamma
   static constexpr bool PRESTATS = PRESTATS_;
@@ -205,39 +200,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     bool ok = true;
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
     PairItem w;
-    // L2 prefetch PF k-blocks ahead of the loads.  The ring holds at most STAGES k-blocks in flight, which covers
-    // an L2 hit but not a trip to DRAM (the first touch of every operand tile): a stage that waits on DRAM stalls
-    // the in-order ring behind it.  The prefetch takes that trip early, without holding a stage.
-    constexpr int PF = Cfg::PREFETCH;
-    auto prefetch_kb = [&](int mt_, int nt_, int kbt) {
-      const bool extra = (kbt >= KB_main);
-      const int kcol = extra ? (kbt - KB_main) * KBW : kbt * KBW;
-      tma_prefetch_l2_2d(extra ? &tm_x2 : &tm_x, kcol, mt_ * 256 + (int)rank * 128);
-      tma_prefetch_l2_2d(extra ? &tm_w2 : &tm_w, kcol, SWIGLU ? (int)rank * p.N + nt_ * 128 : nt_ * BN + (int)rank * (BN / 2));
-    };
     // FP8: the quantised activations are written by the kernel launched just before this one
     if (FP8) grid_dependency_wait();
     for (int i = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i, w); ++i) {
       int mt, nt;
       prefill_tile_coords(w.t, p, mt, nt);
-      [[maybe_unused]] PairItem wn;
-      [[maybe_unused]] int mtn = 0, ntn = 0;
-      [[maybe_unused]] bool have_next = false;
-      if (PF > 0) {
-        have_next = pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i + 1, wn);
-        if (have_next) prefill_tile_coords(wn.t, p, mtn, ntn);
-        if (i == 0 && elect_one())
-          for (int kb = w.kb0; kb < min(w.kb0 + PF, w.kb1); ++kb) prefetch_kb(mt, nt, kb);
-        __syncwarp();
-      }
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
         if (elect_one()) {
-          if (PF > 0) {
-            const int kbt = kb + PF;
-            if (kbt < w.kb1) prefetch_kb(mt, nt, kbt);
-            else if (have_next && wn.kb0 + (kbt - w.kb1) < wn.kb1) prefetch_kb(mtn, ntn, wn.kb0 + (kbt - w.kb1));
-          }
           const bool extra = (kb >= KB_main);
           const int kcol = extra ? (kb - KB_main) * KBW : kb * KBW;
           const uint32_t lead_ready = lead_ready0 + 8u * s;
@@ -431,7 +401,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const int m = mt * 256 + (int)rank * 128 + row;
         r_pre = (p.row_rstd == nullptr) ? 1.0f : ((m < p.M) ? __ldg(p.row_rstd + m) : 0.f);
       }
-      mbar_wait(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, it) &&
+      mbar_wait_long(bar_tfull(acc), aph, ctl, 3, 3 * STAGES + acc, it) &&
           (PRESTATS || mbar_wait(bar_rsfull(acc), aph, ctl, 3, 3 * STAGES + 2 * NACC + acc, it));
       // named barriers have no time limit: one thread decides for the four warps whether to go on
       named_bar_sync(3, 128);

@@ -114,6 +114,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, CtaCtl*
   return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx, 0u);
 }
 
+// A wait that is long by design (an epilogue waiting out a whole main loop): optionally backs off between polls.
+#ifndef RL_LONG_WAIT_SLEEP_NS
+#define RL_LONG_WAIT_SLEEP_NS 0
+#endif
+__device__ __forceinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity, CtaCtl* ctl, int role, int bar_id,
+                                               int idx) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, ctl, role, bar_id, idx, (uint32_t)RL_LONG_WAIT_SLEEP_NS);
+}
+
 // Bounded wait for a counter in global memory to reach `target`.  Only for counters bumped by CTAs of the
 // same launch (a persistent grid no larger than the device holds at once, so every CTA is running or about
 // to).  Same time limit and status record as the barrier waits.
@@ -186,12 +196,6 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
-}
-// Ask for the box at (x, y) of a 2-D tiled tensor to be brought into L2.  No completion to wait for: a later
-// TMA load of the same box then finds it there (or joins the fill in flight) instead of paying DRAM latency
-// while it holds a shared-memory stage.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 // 2-D tiled load global -> shared, completion on an mbarrier of this CTA.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
