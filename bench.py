@@ -55,7 +55,12 @@ WORKLOADS = {
     "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor", False),
     "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor", False),
     "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor", True),   # e4m3 weights + per-channel scales
+    "prefill_m128_128x6144x4096": (128, 6144, 4096, "tensor", False),  # one row tile of tokens: the one-CTA kernel
+    # the neighbouring operators of the reference's tables, for profiling (N = output channels)
+    "swiglu_4096x14336x4096": (4096, 14336, 4096, "tensor", False),    # rmsnorm -> [gate; up] GEMM -> silu(gate) * up
+    "lora_4096x4096x4096": (4096, 4096, 4096, "tensor", False),        # x W^T + (x A^T) B^T, lora_dim 16
 }
+LORA_DIM = 16
 DEFAULT_WORKLOAD = "mlp_16384x57344x8192"
 EXTRA_1GPU = ["prefill_qkv_4096x6144x4096", "decode_1x28672x4096", "decode_4x28672x4096", "decode_16x28672x4096",
               "decode_64x28672x4096", "bf16_8192x14336x4096", "fp8w_8192x14336x4096"]
@@ -278,28 +283,45 @@ def run_reference_arm(args, rank):
 class Runner:
     """One workload on this rank's GPU: buffers, the step, timing windows, parity."""
 
-    def __init__(self, kb, name, dev, rank, world, variant="auto"):
+    def __init__(self, kb, name, dev, rank, world, variant="auto", gamma=True):
         self.kb, self.name, self.dev, self.rank, self.world, self.variant = kb, name, dev, rank, world, variant
         self.M, self.N_total, self.K, self.bound, self.fp8 = WORKLOADS[name]
+        self.op = name.split("_")[0] if name.split("_")[0] in ("swiglu", "lora") else "linear"
+        self.gamma = gamma
         n0, n1 = shard_range(self.N_total, world, rank) if world > 1 else (0, self.N_total)
         self.n0, self.n1, self.N = n0, n1, n1 - n0
         self.step_bytes = algorithmic_bytes(self.M, self.N, self.K, self.fp8)
         self.flops = 2.0 * self.M * self.N * self.K                    # this rank's share
         self.flops_total = 2.0 * self.M * self.N_total * self.K
         self.sets = max(2, -(-2 * L2_BYTES // self.step_bytes))        # rotate enough buffer sets to exceed 2x L2
-        self.bufs = make_buffers(self.M, self.N, self.K, dev, self.sets, seed=18 + 1000 * rank, fp8=self.fp8)
+        self.bufs = make_buffers(self.M, (2 if self.op == "swiglu" else 1) * self.N, self.K, dev, self.sets,
+                                 seed=18 + 1000 * rank, fp8=self.fp8)
+        if self.op == "swiglu":      # W is [2N, K] (gate rows, then up rows), y [M, N]
+            self.bufs = [(x, g, W, y[:, : self.N].contiguous(), w) for (x, g, W, y, w) in self.bufs]
+        if self.op == "lora":
+            gen = torch.Generator(device=dev).manual_seed(5 + rank)
+            self.lA = (torch.randn(LORA_DIM, self.K, generator=gen, device=dev) * self.K ** -0.5).to(torch.bfloat16)
+            self.lB = torch.randn(self.N, LORA_DIM, generator=gen, device=dev).to(torch.bfloat16)
         self.stream = torch.cuda.current_stream()
         self.kernel = "e4m3 pair kernel"
-        if not self.fp8:
+        if self.op != "linear":
+            self.kernel = self.op
+        elif not self.fp8:
             from kernel_benchmarking_b200 import _lib
-            v = _lib.load().rl_select_variant(self.M, self.N, self.K, 1, 1)
+            v = _lib.load().rl_select_variant(self.M, self.N, self.K, 1 if gamma else 0, 1)
             self.kernel = _lib.VARIANT_NAMES.get(v, str(v)) if variant == "auto" else str(variant)
         # kernels launched per step: the pre-pass (row statistics / quantisation) and the GEMM, or one fused kernel
         self.launches_per_step = 2 if (self.fp8 or "prestats" in self.kernel) else 1
 
     def step(self, i):
         x, g, W, y, wsc = self.bufs[i % self.sets]
-        self.kb.rmsnorm_linear(x, g, W, EPS, w_scale=wsc, out=y, variant="auto" if self.fp8 else self.variant)
+        if self.op == "swiglu":
+            self.kb.rmsnorm_swiglu(x, g, W, EPS, out=y)
+        elif self.op == "lora":
+            self.kb.lora_linear(x, W, self.lA, self.lB, out=y)
+        else:
+            self.kb.rmsnorm_linear(x, g if self.gamma else None, W, EPS, w_scale=wsc, out=y,
+                                   variant="auto" if self.fp8 else self.variant)
 
     def barrier(self):
         if self.world > 1:
@@ -405,6 +427,8 @@ def main():
     ap.add_argument("--variant", default="auto", help="kernel variant name (see kernel_benchmarking_b200._lib.VARIANTS)")
     ap.add_argument("--no-extra", action="store_true", help="only the main workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gamma", action="store_true",
+                    help="gamma = None, the reference operator's own form (profiling runs only)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + timed steps of the workload (no clock sampling, e2e, extras or CPU legs): "
                          "the command a profiler wraps")
@@ -430,7 +454,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
 
-    run = Runner(kb, args.workload, dev, rank, world, variant=args.variant)
+    if (args.no_gamma or args.workload.split("_")[0] in ("swiglu", "lora")) and not args.profile:
+        raise SystemExit("--no-gamma and the swiglu / lora workloads are for --profile runs")
+    run = Runner(kb, args.workload, dev, rank, world, variant=args.variant, gamma=not args.no_gamma)
     M, N, K = run.M, run.N, run.K
 
     if args.profile:

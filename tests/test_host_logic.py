@@ -178,3 +178,22 @@ def test_harness_metadata_column():
     assert harness.throughput_metadata(4096, 4096, 4096, None) is None
     row = harness.ExperimentRow("rmsnorm_linear:1:b200", 4096, 4096, 4096, ms_median=0.1, metadata=md)
     assert row.csv().split(",")[11] == md
+
+
+def test_clock_summary_picks_the_samples_under_load():
+    """On a power-capped part the loaded samples are the low clocks: they are chosen by utilisation (or power),
+    never by clock value."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    idle = ["1965", "1965", "0", "180.0", "Not Active", "Not Active", "Not Active", "Not Active"]
+    busy = [[str(c), "1965", "100", "990.0", "Not Active", "Not Active", "Not Active", "Active"] for c in (1320, 1350, 1290, 1410)]
+    out = bench.summarize_clock_samples([idle] * 6 + busy + [idle] * 6)
+    assert out["sm_mhz"] == 1335.0 and out["sm_mhz_min"] == 1290.0 and out["sm_max_mhz"] == 1965.0
+    assert out["reasons"] == ["sw_power_cap"] and out["samples_under_load"] == 4 and out["samples"] == 16
+    # a region too short for the utilisation counter: fall back on power draw
+    lag = [[str(c), "1965", "3", "950.0", "Not Active", "Not Active", "Not Active", "Active"] for c in (1500, 1480)]
+    out = bench.summarize_clock_samples([idle] * 4 + lag)
+    assert out["sm_mhz"] == 1490.0 and out["loaded_by"].startswith("power")
+    assert bench.summarize_clock_samples([])["sm_mhz"] is None
