@@ -87,7 +87,7 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const voi
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of on every call.
 template <class KernelFn>
-cudaError_t set_smem_once(KernelFn fn, int bytes) {
+cudaError_t set_smem_once(KernelFn fn, int bytes, bool max_carveout = false) {
   // keyed by the kernel's address: every instantiation with the same signature shares this function
   static std::mutex mu;
   static const void* seen[64][64];
@@ -101,6 +101,9 @@ cudaError_t set_smem_once(KernelFn fn, int bytes) {
   for (int i = 0; i < n_seen[dev]; ++i)
     if (seen[dev][i] == key) return cudaSuccess;
   e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  // a kernel sized for several CTAs per SM needs the whole shared-memory carve-out to get them
+  if (e == cudaSuccess && max_carveout)
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
   if (e == cudaSuccess && n_seen[dev] < 64) seen[dev][n_seen[dev]++] = key;
   return e;
 }
@@ -243,16 +246,16 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
 
 // Row tiles (of 256 tokens) per sweep group.  Tiles are walked group by group, a group's row tiles against every
 // column tile, so the x rows of one group stay in L2 while W streams past; W is read from DRAM once per group.
-// The group is made as large as fits a budget well inside the 126 MB L2 (x of the group, the W tiles in flight
-// and the y tiles on their way out share it): when all of x fits, W streams exactly once.
-#ifndef RL_GROUP_BUDGET_MB
-#define RL_GROUP_BUDGET_MB 40
-#endif
+// Two limits.  The group's x rows must fit a budget well inside the 126 MB L2 (the W tiles in flight and the y
+// tiles on their way out share it).  And the 74 pairs running at a time should cover a near-square patch of
+// tiles (about 8-10 row tiles by as many column tiles): a taller group makes them touch more distinct operand
+// tiles at once, and the e4m3 kernel measured 5-6 % slower with 32 row tiles per group than with 8, although W
+// then streamed from DRAM only once.  Measured on 16384 x 7168 x 8192: groups of 10 beat groups of 8 by 2 %.
+constexpr int RL_GROUP_BUDGET_MB = 40;
+constexpr int RL_GROUP_MAX = 10;
 int pick_group_m(int m_tiles, long long row_tile_bytes) {
-#ifdef RL_GROUP_M_FIXED
-  return RL_GROUP_M_FIXED;
-#endif
   long long g = ((long long)RL_GROUP_BUDGET_MB << 20) / (row_tile_bytes > 0 ? row_tile_bytes : 1);
+  if (g > RL_GROUP_MAX) g = RL_GROUP_MAX;
   if (g < 4) g = 4;
   if (g > m_tiles) g = m_tiles;
   const long long groups = (m_tiles + g - 1) / g;  // even the groups out
@@ -363,6 +366,14 @@ int launch_prefill_pair(const PairArgs& a) {
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 
+// The 16-token configuration of the small-M kernel: <tokens, ring stages, transform warps, CTAs per SM>.
+#ifndef RL_DEC16_STAGES
+#define RL_DEC16_STAGES 8
+#define RL_DEC16_TW 4
+#define RL_DEC16_MINB 1
+#endif
+using DecodeCfg16 = DecodeCfg<16, RL_DEC16_STAGES, RL_DEC16_TW, RL_DEC16_MINB>;
+
 template <class Cfg>
 int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                   int64_t ldx, int64_t ldw, int64_t ldy, float eps, uint8_t* ws, const WsLayout& wl, int sms,
@@ -387,11 +398,13 @@ int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void
   p.partials = reinterpret_cast<float*>(ws + wl.partials_off);
   int grid = sms < RL_MAX_CTAS ? sms : RL_MAX_CTAS;
   if (units < grid) grid = (int)units;
-  // every CTA owns floor(tiles / grid) tiles whole; the k-loops of the other tiles are shared out evenly
-  p.whole_per_cta = p.n_tiles / grid;
+  // every CTA owns floor(tiles / grid) tiles whole; the k-loops of the other tiles are shared out evenly.
+  // Only in the 16-token configuration: measured, it gains 0.6 % there and costs 6 % at 64 tokens, where the
+  // plain contiguous split (every tile's k-loop shared) is kept.
+  p.whole_per_cta = (Cfg::MPAD <= 16) ? p.n_tiles / grid : 0;
   p.sk_tiles = p.n_tiles - p.whole_per_cta * grid;
   p.units_total = p.sk_tiles * p.KB;
-  cudaError_t e = set_smem_once(decode_kernel<Cfg>, Cfg::SMEM_BYTES);
+  cudaError_t e = set_smem_once(decode_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::MINB > 1);
   if (e != cudaSuccess) return cuda_err(e);
   // Programmatic stream serialisation: this grid's prologue (barrier setup, tensor-memory allocation,
   // descriptor fetch) may overlap the tail of the previous kernel in the stream.  The kernel touches no
@@ -431,7 +444,9 @@ int launch_rowquant(const void* x, const void* gamma, void* q, float* row_scale,
   p.q = reinterpret_cast<uint8_t*>(q);
   p.row_scale = row_scale;
   p.M = M; p.K = K; p.ldx = ldx; p.ldq = ldq; p.eps = eps;
-  rowquant_kernel<<<M, 128, 0, st>>>(p);
+  if (K <= 4096) rowquant_kernel<128><<<M, 128, 0, st>>>(p);
+  else if (K <= 8192) rowquant_kernel<256><<<M, 256, 0, st>>>(p);
+  else rowquant_kernel<512><<<M, 512, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
@@ -484,7 +499,8 @@ int static_scratch_address(uint8_t** out) {
 // What RL_VARIANT_AUTO runs for a bf16 call.
 int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms) {
   if (M <= 64) return RL_VARIANT_DECODE;
-  if (M <= 128) return RL_VARIANT_PREFILL_TS_N192;
+  // 64 < M <= 128 runs on the CTA-pair kernel as well (half of each 256-row tile is padding, but the tiles can be
+  // cut along K over all pairs: measured 20-30 % faster than one CTA per 128 x 192 tile, which leaves SMs idle)
   // Without gamma (the reference operator) x needs no fold: the MMA reads it straight from shared memory,
   // which frees tensor memory for a second accumulator.
   // Row statistics: from the overlapped pre-pass when there is a workspace and more than one round of tiles
@@ -583,7 +599,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
 
   if (decode) {
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-    if (M <= 16) return launch_decode<DecodeCfg<16, 12>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
+    if (M <= 16) return launch_decode<DecodeCfg16>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
     if (M <= 32) return launch_decode<DecodeCfg<32, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
     return launch_decode<DecodeCfg<64, 8>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, ws, wl, di.sms, st);
   }
@@ -687,7 +703,7 @@ int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void*
   // at zero; partial tiles are always written before they are read and need no clearing.
   cudaError_t e = cudaMemsetAsync(scratch, 0, wl.ssq_off, st);
   if (e != cudaSuccess) return cuda_err(e);
-  return launch_decode<DecodeCfg<16, 12>>(x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw,
+  return launch_decode<DecodeCfg16>(x, reinterpret_cast<const __nv_bfloat16*>(gamma), W, y, M, N, K, ldx, ldw,
                                           ldy, eps, scratch, wl, di.sms, st);
 }
 

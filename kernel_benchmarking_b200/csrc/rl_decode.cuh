@@ -16,8 +16,13 @@
 // and stores y.  No CTA ever waits for another.  Counters are left at zero for
 // the next launch.
 //
-// Warp roles: 0 TMA producer, 1 UMMA issuer, 2-5 transform (sum of squares via
-// warp shuffles + gamma fold in shared memory), 6-9 epilogue.
+// Warp roles: 0 TMA producer, 1 UMMA issuer, then TW transform warps (sum of squares via
+// warp shuffles + gamma fold in shared memory), then 4 epilogue warps.
+//
+// Ring depth, measured on 28672 x 4096 with 16 tokens: 8 stages stream 2-3 % faster than 12 (less to
+// fill and drain per launch), 6 are 1 % slower than 8, 4 are 10 % slower.  A configuration sized for
+// two CTAs per SM (6 stages, 2 transform warps, 256 threads), so that the next launch's CTAs could
+// set up on the free half while this launch drains, measured the same as with one CTA per SM.
 #pragma once
 #include "rl_ptx.cuh"
 
@@ -39,10 +44,12 @@ struct DecodeParams {
   float* ssq_partials;  // [grid][2][MPAD]
 };
 
-template <int MPAD_, int STAGES_>
+template <int MPAD_, int STAGES_, int TW_ = 4, int MINB_ = 1>
 struct DecodeCfg {
   static constexpr int MPAD = MPAD_, STAGES = STAGES_;
-  static constexpr int THREADS = 320;
+  static constexpr int TW = TW_;      // transform warps; units are dealt to them round-robin
+  static constexpr int MINB = MINB_;  // CTAs per SM the kernel is compiled (and sized) for
+  static constexpr int THREADS = 64 + 32 * TW + 128;
   static constexpr int W_BYTES = 128 * 64 * 2;
   static constexpr int X_BYTES = MPAD * 64 * 2;
   static constexpr int G_BYTES = 128;
@@ -50,7 +57,7 @@ struct DecodeCfg {
   static constexpr int OFF_X = OFF_W + STAGES * W_BYTES;
   static constexpr int OFF_G = OFF_X + STAGES * X_BYTES;
   static constexpr int OFF_SSQ = OFF_G + STAGES * G_BYTES;
-  static constexpr int OFF_RVEC = OFF_SSQ + 4 * 2 * MPAD * 4;
+  static constexpr int OFF_RVEC = OFF_SSQ + TW * 2 * MPAD * 4;
   static constexpr int OFF_BAR = OFF_RVEC + MPAD * 4;
   static constexpr int NUM_BARS = 3 * STAGES + 6;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
@@ -59,10 +66,11 @@ struct DecodeCfg {
   static constexpr int NCH = MPAD / 4;  // 16-byte chunks of the x tile per lane of the warp that transforms a unit
   static_assert(MPAD == 16 || MPAD == 32 || MPAD == 64, "MPAD");
   static_assert(X_BYTES % 1024 == 0, "x stage alignment");
-  // units are dealt to the 4 transform warps round-robin; a ring slot must always belong to the same
+  // units are dealt to the transform warps round-robin; a ring slot must always belong to the same
   // warp, or a warp that skipped a slot's previous phase could mistake it for its own (parity aliasing)
-  static_assert(STAGES % 4 == 0, "STAGES must be a multiple of 4");
-  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+  static_assert(TW >= 1 && TW <= 4 && STAGES % TW == 0, "STAGES must be a multiple of the transform warps");
+  // (the four epilogue warps follow the transform warps: any four consecutive warps cover the four lane quarters of tensor memory)
+  static_assert(SMEM_BYTES * MINB + 1024 * MINB <= 233472, "shared memory budget for MINB CTAs per SM");
 };
 
 // Balanced contiguous split of `total` units over `G` CTAs.
@@ -107,10 +115,10 @@ struct DecodeSegments {
 };
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const DecodeParams p) {
-  constexpr int MPAD = Cfg::MPAD, STAGES = Cfg::STAGES, NCH = Cfg::NCH;
+  constexpr int MPAD = Cfg::MPAD, STAGES = Cfg::STAGES, NCH = Cfg::NCH, TW = Cfg::TW;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -125,7 +133,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   volatile int* epi_go = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 8);
   volatile int* epi_last = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC + 12);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(smem + Cfg::OFF_MISC + 16);
-  float* ssq = reinterpret_cast<float*>(smem + Cfg::OFF_SSQ);    // [4 warps][2][MPAD] partial sums of squares
+  float* ssq = reinterpret_cast<float*>(smem + Cfg::OFF_SSQ);    // [TW warps][2][MPAD] partial sums of squares
   float* rvec = reinterpret_cast<float*>(smem + Cfg::OFF_RVEC);  // [MPAD] 1/rms per token of the tile being finished
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,7 +164,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull(a), 1);
       mbar_init(bar_tempty(a), 4);
-      mbar_init(bar_rs(a), 4);
+      mbar_init(bar_rs(a), TW);
     }
     ctl->abort = 0;
     ctl->status = p.status;
@@ -241,11 +249,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         u += n_units;
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + TW) {
     // ------------------------------------------------------------ transform
     // The x tile of one unit is small (MPAD x 128 bytes), so one warp handles a whole unit and
-    // the four warps take units round-robin: four units are in flight in this role at once.
-    const int tw = warp - 2;     // 0..3
+    // the TW warps take units round-robin: TW units are in flight in this role at once.
+    const int tw = warp - 2;     // 0..TW-1
     const int c = lane & 7;      // 16-byte chunk within the 128-byte row
     bool ok = true;
     int u = 0;  // running unit count of the CTA = ring position of the segment's first unit
@@ -258,7 +266,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 #pragma unroll
       for (int i = 0; i < NCH; ++i) ss[i] = 0.f;
       const int j0 = u;
-      for (int i = ((tw - j0) % 4 + 4) % 4; i < n_units; i += 4) {
+      for (int i = ((tw - j0) % TW + TW) % TW; i < n_units; i += TW) {
         const int j = j0 + i;
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
@@ -320,7 +328,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
-    const int epi_tid = threadIdx.x - 192;
+    const int epi_tid = threadIdx.x - (64 + 32 * TW);
     const float inv_k = 1.0f / (float)p.K;
     for (int seg = 0; seg < segs.nseg; ++seg) {
       int nat, tile, kb0, n_units;
@@ -347,11 +355,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       }
       const int n = tile * 128 + n_local;
       const bool whole = (n_units == KB);
-      // one thread per token adds up the four transform warps' shares of the sum of squares
+      // one thread per token adds up the transform warps' shares of the sum of squares
       float tot = 0.f;
       if (epi_tid < MPAD) {
 #pragma unroll
-        for (int w = 0; w < 4; ++w) tot += ssq[(w * 2 + acc) * MPAD + epi_tid];
+        for (int w = 0; w < TW; ++w) tot += ssq[(w * 2 + acc) * MPAD + epi_tid];
       }
       bool finish = whole;
       if (whole) {

@@ -631,7 +631,7 @@ def test_auto_whole_never_splits_and_matches():
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 1, 1)] == "prefill_pair_prestats"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 0, 1)] == "prefill_pair_direct_prestats"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(16, 28672, 4096, 1, 1)] == "decode"
-    assert _lib.VARIANT_NAMES[lib.rl_select_variant(100, 512, 512, 1, 1)] == "prefill_ts_n192"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(100, 512, 512, 1, 1)] == "prefill_pair_prestats"
 
 
 @pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason="needs two GPUs")
