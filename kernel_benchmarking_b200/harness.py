@@ -259,6 +259,8 @@ def parse_new_style(argv=None) -> argparse.Namespace:
     ap.add_argument("--shapes", default="gemm", choices=["gemm", "extra"],
                     help="gemm: python/workload_shapes.py GEMM_SHAPES; extra: res/cdsl_rmsnorm_shapes_m128n256.txt")
     ap.add_argument("--header", action="store_true", help="print the CSV header (demo/gen_header.py) and exit")
+    ap.add_argument("--pause", type=float, default=2.0,
+                    help="seconds of rest between kernels (the reference sleeps 2 s) and, with --all, 1.5 x that between configs")
     ap.add_argument("--all", action="store_true",
                     help="every config of the shape table, one process each, into --csv (run_scripts/profile_rmsnorm_linear.sh)")
     return ap.parse_args(argv)
@@ -311,7 +313,7 @@ def run_old_style(ns: argparse.Namespace, out=print) -> list:
 
 
 def run_all(csv_path: str, shapes: str = "gemm", workload: str = "rmsnorm_linear", pause_s: float = 3.0,
-            runner=None) -> int:
+            runner=None, kernel_pause_s: float = 2.0) -> int:
     """The batch driver (run_scripts/profile_rmsnorm_linear.sh:6-17): write the header into the CSV (overwriting
     it), then one process per config appending its rows, a pause between them.  The reference's loop runs one
     index past its 10-row table; this one stops at the last row."""
@@ -327,7 +329,7 @@ def run_all(csv_path: str, shapes: str = "gemm", workload: str = "rmsnorm_linear
     failed = 0
     for i in range(n):
         cmd = [sys.executable, "-m", "kernel_benchmarking_b200.harness", str(i), "--csv", csv_path, "--shapes", shapes,
-               "--workload", workload]
+               "--workload", workload, "--pause", str(kernel_pause_s)]
         rc = runner(cmd) if runner is not None else subprocess.run(cmd).returncode
         failed += 1 if rc else 0
         if runner is None and i + 1 < n:
@@ -350,12 +352,12 @@ def main(argv=None) -> None:
     if ns.all:
         csv_path = ns.csv or time.strftime("results/rmsnorm_linear_%Y%m%d_%H%M%S.csv")
         print(f"writing csv to {csv_path}")
-        raise SystemExit(1 if run_all(csv_path, ns.shapes, ns.workload) else 0)
+        raise SystemExit(1 if run_all(csv_path, ns.shapes, ns.workload, pause_s=1.5 * ns.pause, kernel_pause_s=ns.pause) else 0)
     shapes = EXTRA_SHAPES if ns.shapes == "extra" else RMSNORM_LINEAR_SHAPES
     job = lora_job(ns.config) if ns.workload == "lora" else rmsnorm_linear_job(ns.config, shapes=shapes)
     if ns.shapes == "extra":
         job.workload = "rmsnorm_linear_extra"
-    write_rows(job.run(ncu=ns.ncu), ns.csv)
+    write_rows(job.run(ncu=ns.ncu, pause_s=ns.pause), ns.csv)
 
 
 if __name__ == "__main__":
