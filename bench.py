@@ -55,7 +55,8 @@ WORKLOADS = {
     "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor", False),
     "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor", False),
     "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor", True),   # e4m3 weights + per-channel scales
-    "prefill_m128_128x6144x4096": (128, 6144, 4096, "tensor", False),  # one row tile of tokens: the one-CTA kernel
+    "fp8w_decode_16x28672x4096": (16, 28672, 4096, "hbm", True),   # e4m3 weights at decode size: half the bytes
+    "prefill_m128_128x6144x4096": (128, 6144, 4096, "tensor", False),  # half a row tile of tokens
     # the neighbouring operators of the reference's tables, for profiling (N = output channels)
     "swiglu_4096x14336x4096": (4096, 14336, 4096, "tensor", False),    # rmsnorm -> [gate; up] GEMM -> silu(gate) * up
     "lora_4096x4096x4096": (4096, 4096, 4096, "tensor", False),        # x W^T + (x A^T) B^T, lora_dim 16
@@ -63,13 +64,17 @@ WORKLOADS = {
 LORA_DIM = 16
 DEFAULT_WORKLOAD = "mlp_16384x57344x8192"
 EXTRA_1GPU = ["prefill_qkv_4096x6144x4096", "decode_1x28672x4096", "decode_4x28672x4096", "decode_16x28672x4096",
-              "decode_64x28672x4096", "bf16_8192x14336x4096", "fp8w_8192x14336x4096"]
+              "decode_64x28672x4096", "bf16_8192x14336x4096", "fp8w_8192x14336x4096", "fp8w_decode_16x28672x4096"]
 EXTRA_MULTI = ["fp8w_8192x14336x4096"]
 # DRAM bytes (read + written) per launch of the dominant kernel, from one profiler capture each, keyed by the
 # kernel variant and the per-GPU shape it was captured on.  A run whose variant or shape is not listed reports null.
 MEASURED_DRAM_BYTES = {
-    ("prefill_pair_prestats", 4096, 6144, 4096): 164.4e6,
-    ("decode", 16, 28672, 4096): 240.3e6,
+    ("prefill_pair_prestats", 4096, 6144, 4096): 128.0e6,
+    ("prefill_pair_prestats", 16384, 7168, 8192): 2230.5e6,
+    ("e4m3 pair kernel", 8192, 14336, 4096): 314.0e6,       # the GEMM kernel; the quantisation pre-pass adds 74 MB
+    ("decode", 1, 28672, 4096): 238.8e6,
+    ("decode", 16, 28672, 4096): 239.9e6,
+    ("decode", 64, 28672, 4096): 243.1e6,
 }
 L2_BYTES = 126 * 1024 * 1024
 WINDOWS = 5
@@ -303,7 +308,7 @@ class Runner:
             self.lA = (torch.randn(LORA_DIM, self.K, generator=gen, device=dev) * self.K ** -0.5).to(torch.bfloat16)
             self.lB = torch.randn(self.N, LORA_DIM, generator=gen, device=dev).to(torch.bfloat16)
         self.stream = torch.cuda.current_stream()
-        self.kernel = "e4m3 pair kernel"
+        self.kernel = "e4m3 pair kernel" if self.M > 64 else "e4m3 decode"
         if self.op != "linear":
             self.kernel = self.op
         elif not self.fp8:

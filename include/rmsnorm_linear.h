@@ -124,6 +124,8 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
  *   q = e4m3(x * gamma * 448 / amax_m); y = (q @ Wq^T) * rsqrt(mean x^2 + eps) * amax_m / 448 * w_scale[n].
  *   K and ldw must be multiples of 16.  The workspace (rl_workspace_bytes with RL_W_E4M3) holds
  *   the quantised activations, the per-token scales and the partial blocks of a k-split last round.
+ *   M <= 64 (memory bound on the weights, which e4m3 halves) runs the operand-swapped stream-K kernel on the
+ *   quantised activations; larger M the CTA-pair kernel.
  *   `variant`: RL_VARIANT_AUTO or RL_VARIANT_AUTO_WHOLE.
  * No reference counterpart: the reference project has no quantised path; the operator semantics
  * are those of rl_rmsnorm_linear_bf16 applied to the dequantised weights. */

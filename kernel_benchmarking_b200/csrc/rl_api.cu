@@ -374,22 +374,29 @@ int launch_prefill_pair(const PairArgs& a) {
 #endif
 using DecodeCfg16 = DecodeCfg<16, RL_DEC16_STAGES, RL_DEC16_TW, RL_DEC16_MINB>;
 
+// x / W: bf16, or (FP8 configuration) the e4m3 activations from rowquant_kernel and the e4m3 weights, with the
+// per-token and per-channel scales the epilogue applies.
 template <class Cfg>
 int launch_decode(const void* x, const __nv_bfloat16* gamma, const void* W, void* y, int M, int N, int K,
                   int64_t ldx, int64_t ldw, int64_t ldy, float eps, uint8_t* ws, const WsLayout& wl, int sms,
-                  cudaStream_t st) {
+                  cudaStream_t st, const float* row_scale = nullptr, const float* w_scale = nullptr) {
   CUtensorMap tw, tx;
   int rc;
-  if ((rc = make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, K, N, ldw, 64, 128))) return rc;
-  if ((rc = make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, M, ldx, 64, Cfg::MPAD))) return rc;
+  const CUtensorMapDataType dt = Cfg::FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int eb = Cfg::FP8 ? 1 : 2;
+  if (Cfg::FP8 && (!row_scale || !w_scale)) return RL_ERR_NULL_POINTER;
+  if ((rc = make_map(&tw, dt, eb, W, K, N, ldw, Cfg::KBW, 128))) return rc;
+  if ((rc = make_map(&tx, dt, eb, x, K, M, ldx, Cfg::KBW, Cfg::MPAD))) return rc;
   DecodeParams p{};
   p.M = M; p.N = N; p.K = K; p.eps = eps;
   p.gamma = gamma;
+  p.row_scale = row_scale;
+  p.w_scale = w_scale;
   p.y = reinterpret_cast<__nv_bfloat16*>(y);
   p.ldy = ldy;
   p.n_tiles = (N + 127) / 128;
   if (p.n_tiles > RL_MAX_DECODE_TILES) return RL_ERR_BAD_SHAPE;
-  p.KB = (K + 63) / 64;
+  p.KB = (K + Cfg::KBW - 1) / Cfg::KBW;
   const long long units = (long long)p.n_tiles * p.KB;
   if (units > 0x7fffffffLL) return RL_ERR_BAD_SHAPE;
   p.status = reinterpret_cast<int*>(ws);
@@ -662,7 +669,8 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
     return RL_ERR_ALIGNMENT;
   if (variant != RL_VARIANT_AUTO && variant != RL_VARIANT_AUTO_WHOLE) return RL_ERR_BAD_VARIANT;
   const Fp8WsLayout wl = fp8_ws_layout(M, K);
-  if (!workspace || workspace_bytes < wl.min_total) return RL_ERR_WORKSPACE;
+  // M <= 64 runs the stream-K kernel, whose partial tiles live where the large-M kernel keeps its k-split blocks
+  if (!workspace || workspace_bytes < (M <= 64 ? wl.total : wl.min_total)) return RL_ERR_WORKSPACE;
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
@@ -672,6 +680,23 @@ int rl_rmsnorm_linear_fp8w(const void* x, const void* gamma, const void* Wq, con
   float* row_scale = reinterpret_cast<float*>(ws + wl.row_scale_off);
   uint8_t* xq = ws + wl.xq_off;
   if ((rc = launch_rowquant(x, gamma, xq, row_scale, M, K, ldx, K, eps, st))) return rc;
+  if (M <= 64) {
+    // small M: memory bound on the weights, which e4m3 halves.  The operand-swapped stream-K kernel on the
+    // quantised activations; its counters sit in the region every layout keeps at the same place.
+    WsLayout dl{};
+    dl.counters_off = STATUS_BYTES;
+    dl.ssq_off = wl.row_scale_off;      // not used by the FP8 configuration
+    dl.partials_off = wl.tail_off;
+    static_assert(TAIL_BYTES >= (size_t)RL_MAX_CTAS * 2 * 64 * 128 * 4, "the k-split region holds the stream-K partial tiles");
+    if (M <= 16)
+      return launch_decode<DecodeCfg<16, RL_DEC16_STAGES, RL_DEC16_TW, RL_DEC16_MINB, true>>(
+          xq, nullptr, Wq, y, M, N, K, K, ldw, ldy, eps, ws, dl, di.sms, st, row_scale, w_scale);
+    if (M <= 32)
+      return launch_decode<DecodeCfg<32, 8, 4, 1, true>>(xq, nullptr, Wq, y, M, N, K, K, ldw, ldy, eps, ws, dl, di.sms, st,
+                                                         row_scale, w_scale);
+    return launch_decode<DecodeCfg<64, 8, 4, 1, true>>(xq, nullptr, Wq, y, M, N, K, K, ldw, ldy, eps, ws, dl, di.sms, st,
+                                                       row_scale, w_scale);
+  }
   PairArgs pa;
   pa.x = xq; pa.W = Wq; pa.y = y;
   pa.M = M; pa.N = N; pa.K = K; pa.ldx = K; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;

@@ -42,11 +42,20 @@ struct DecodeParams {
   int* counters;        // [n_tiles], zero between launches
   float* partials;      // [grid][2][MPAD][128]
   float* ssq_partials;  // [grid][2][MPAD]
+  // FP8 configuration: x is the e4m3 activation matrix from rowquant_kernel, W the e4m3 weights
+  const float* row_scale;  // [M] rsqrt(mean x^2 + eps) * amax / 448 per token
+  const float* w_scale;    // [N] per-output-channel weight scales
 };
 
-template <int MPAD_, int STAGES_, int TW_ = 4, int MINB_ = 1>
+template <int MPAD_, int STAGES_, int TW_ = 4, int MINB_ = 1, bool FP8_ = false>
 struct DecodeCfg {
   static constexpr int MPAD = MPAD_, STAGES = STAGES_;
+  // FP8: e4m3 weights and per-token e4m3 activations (quantised beforehand by rowquant_kernel), kind::f8f6f4
+  // MMAs; a k-block is 128 elements (the same 128 bytes per tile row), gamma and the row statistics are already
+  // inside the activations and their per-token scale, so the transform warps only pass the tiles on, and the
+  // epilogue multiplies by row_scale[m] * w_scale[n].  Half the weight bytes of the bf16 kernel per launch.
+  static constexpr bool FP8 = FP8_;
+  static constexpr int KBW = FP8_ ? 128 : 64;  // elements per k-block
   static constexpr int TW = TW_;      // transform warps; units are dealt to them round-robin
   static constexpr int MINB = MINB_;  // CTAs per SM the kernel is compiled (and sized) for
   static constexpr int THREADS = 64 + 32 * TW + 128;
@@ -118,7 +127,8 @@ template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const DecodeParams p) {
-  constexpr int MPAD = Cfg::MPAD, STAGES = Cfg::STAGES, NCH = Cfg::NCH, TW = Cfg::TW;
+  constexpr int MPAD = Cfg::MPAD, STAGES = Cfg::STAGES, NCH = Cfg::NCH, TW = Cfg::TW, KBW = Cfg::KBW;
+  constexpr bool FP8 = Cfg::FP8;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -141,7 +151,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
   const int u_begin = sk_begin(cta, p.units_total, G);
   const int u_end = sk_begin(cta + 1, p.units_total, G);
-  const bool has_gamma = (p.gamma != nullptr);
+  const bool has_gamma = !FP8 && (p.gamma != nullptr);
   const DecodeSegments segs(u_begin, u_end, KB, p.sk_tiles + cta, p.whole_per_cta, G);
 
   // one unit's loads: W tile (streamed once: evict-first), x tile (re-read by every CTA: evict-last), gamma slice
@@ -149,8 +159,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     const int kvalid = min(64, p.K - kb * 64);
     const uint32_t gbytes = has_gamma ? (uint32_t)kvalid * 2u : 0u;
     mbar_expect_tx(bar_full(s), Cfg::W_BYTES + Cfg::X_BYTES + gbytes);
-    tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * 64, tile * 128, pol_w);
-    tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * 64, 0, pol_x);
+    tma_load_2d_hint(sbase + Cfg::OFF_W + s * Cfg::W_BYTES, &tm_w, bar_full(s), kb * KBW, tile * 128, pol_w);
+    tma_load_2d_hint(sbase + Cfg::OFF_X + s * Cfg::X_BYTES, &tm_x, bar_full(s), kb * KBW, 0, pol_x);
     if (gbytes) bulk_load_1d(sbase + Cfg::OFF_G + s * Cfg::G_BYTES, p.gamma + kb * 64, gbytes, bar_full(s));
   };
   const int n_pre = min(STAGES, segs.units());  // units whose loads go out before the CTA-wide sync
@@ -217,7 +227,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
     {
-      constexpr uint32_t idesc = make_idesc(128, MPAD, 1, 1);
+      constexpr uint32_t idesc = FP8 ? make_idesc(128, MPAD, 0, 0) : make_idesc(128, MPAD, 1, 1);
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -238,7 +248,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
           const uint64_t bdesc = make_sw128_kmajor_desc(sbase + Cfg::OFF_X + s * Cfg::X_BYTES);
           if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+            for (int k = 0; k < 4; ++k) {
+              if (FP8) umma_f8_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+              else umma_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+            }
             umma_commit(bar_empty(s));
           }
           __syncwarp();
@@ -273,6 +286,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         ok = mbar_wait(bar_full(s), ph, ctl, 2, s, u + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (FP8) {  // nothing to fold and nothing to sum: hand the tile on
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_xf(s));
+          continue;
+        }
         uint8_t* xt = smem + Cfg::OFF_X + s * Cfg::X_BYTES;
         const int kvalid = p.K - (kb0 + i) * 64;
         uint4 gv = make_uint4(0, 0, 0, 0);
@@ -355,6 +373,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       }
       const int n = tile * 128 + n_local;
       const bool whole = (n_units == KB);
+      [[maybe_unused]] float wsn = 1.0f;  // FP8: this thread's channel scale
+      if (FP8) wsn = (n < p.N) ? __ldg(p.w_scale + n) : 0.f;
       // one thread per token adds up the transform warps' shares of the sum of squares
       float tot = 0.f;
       if (epi_tid < MPAD) {
@@ -363,14 +383,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       }
       bool finish = whole;
       if (whole) {
-        if (epi_tid < MPAD) rvec[epi_tid] = 1.0f / sqrtf(tot * inv_k + p.eps);
+        if (epi_tid < MPAD)
+          rvec[epi_tid] = FP8 ? ((epi_tid < p.M) ? __ldg(p.row_scale + epi_tid) : 0.f) : 1.0f / sqrtf(tot * inv_k + p.eps);
         named_bar_sync(1, 128);
       } else {
         const int slot = (nat == 0) ? 0 : 1;  // slot 0: the tile this CTA's run starts in
         float* part = p.partials + (size_t)(cta * 2 + slot) * MPAD * 128;
 #pragma unroll
         for (int m = 0; m < MPAD; ++m) part[m * 128 + n_local] = a[m];
-        if (epi_tid < MPAD) p.ssq_partials[(cta * 2 + slot) * MPAD + epi_tid] = tot;
+        if (!FP8 && epi_tid < MPAD) p.ssq_partials[(cta * 2 + slot) * MPAD + epi_tid] = tot;
         __threadfence();
         named_bar_sync(1, 128);
         const int first = sk_cta_of_unit(tile * KB, p.units_total, G);
@@ -395,11 +416,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
             float ld[MPAD];
 #pragma unroll
             for (int m = 0; m < MPAD; ++m) ld[m] = __ldcg(cpart + m * 128 + n_local);
-            if (epi_tid < MPAD) s2 += __ldcg(p.ssq_partials + (cc * 2 + cslot) * MPAD + epi_tid);
+            if (!FP8 && epi_tid < MPAD) s2 += __ldcg(p.ssq_partials + (cc * 2 + cslot) * MPAD + epi_tid);
 #pragma unroll
             for (int m = 0; m < MPAD; ++m) a[m] += ld[m];
           }
-          if (epi_tid < MPAD) rvec[epi_tid] = 1.0f / sqrtf(s2 * inv_k + p.eps);
+          if (epi_tid < MPAD)
+            rvec[epi_tid] = FP8 ? ((epi_tid < p.M) ? __ldg(p.row_scale + epi_tid) : 0.f) : 1.0f / sqrtf(s2 * inv_k + p.eps);
           named_bar_sync(5, 128);
         }
       }
@@ -407,7 +429,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         if (n < p.N) {
 #pragma unroll
           for (int m = 0; m < MPAD; ++m)
-            if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(a[m] * rvec[m]);
+            if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(FP8 ? a[m] * rvec[m] * wsn : a[m] * rvec[m]);
         }
       }
       // accumulator and ssq[acc] fully consumed

@@ -401,6 +401,25 @@ def test_fp8_tail_tiles_split_along_k(M, N, K):
         assert torch.equal(kb.rmsnorm_linear(xd, gd, Wqd, 1e-6, w_scale=wsd), y)
 
 
+@pytest.mark.parametrize("M", [1, 16, 33, 64])
+def test_fp8_small_m_runs_the_stream_k_kernel(M):
+    """e4m3 weights with M <= 64 (the memory-bound case, where e4m3 halves the bytes): the operand-swapped stream-K
+    kernel on per-token quantised activations, at the decode benchmark's width."""
+    N, K = 28672, 4096
+    x, gm, W = orc.make_inputs(M, N, K, seed=40 + M)
+    Wq, w_scale = orc.quantize_weight_e4m3(W)
+    y = run_fp8(x, gm, Wq, w_scale, 1e-6)
+    assert y.shape == (M, N)
+    assert orc.rel_max_err(y, orc.reference_fp32(x, gm, Wq, 1e-6, w_scale=w_scale)) <= FP8_TOL_SMALL_K
+    assert orc.rel_max_err(y, orc.fp8_kernel_model(x, gm, Wq, w_scale, 1e-6).float()) <= 1e-2
+    assert torch.equal(run_fp8(x, gm, Wq, w_scale, 1e-6), y)
+    # the same rows through the large-M kernel (padded to 128 tokens) agree to bf16 rounding
+    xp = torch.zeros(128, K, dtype=torch.bfloat16)
+    xp[:M] = x
+    yp = run_fp8(xp, gm, Wq, w_scale, 1e-6)[:M]
+    assert orc.rel_max_err(yp, y.float()) <= 1e-2
+
+
 def test_config5_fp8_weights():
     M, N, K = 8192, 14336, 4096
     g = torch.Generator().manual_seed(18)
