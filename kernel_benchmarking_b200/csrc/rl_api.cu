@@ -247,12 +247,13 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
 // Row tiles (of 256 tokens) per sweep group.  Tiles are walked group by group, a group's row tiles against every
 // column tile, so the x rows of one group stay in L2 while W streams past; W is read from DRAM once per group.
 // Two limits.  The group's x rows must fit a budget well inside the 126 MB L2 (the W tiles in flight and the y
-// tiles on their way out share it).  And the 74 pairs running at a time should cover a near-square patch of
-// tiles (about 8-10 row tiles by as many column tiles): a taller group makes them touch more distinct operand
-// tiles at once, and the e4m3 kernel measured 5-6 % slower with 32 row tiles per group than with 8, although W
-// then streamed from DRAM only once.  Measured on 16384 x 7168 x 8192: groups of 10 beat groups of 8 by 2 %.
+// tiles on their way out share it).  And the 74 pairs running at a time should cover a patch of tiles that is not
+// too far from square: a taller group makes them touch more distinct operand tiles at once.  Measured: on
+// 16384 x 7168 x 8192 groups of 10 beat groups of 8 by 2 %; groups of 8, 10 and 16 time the same on the 4096- and
+// 8192-token shapes while 16 halves the weight re-reads; groups of 32 ran the e4m3 kernel 5-6 % slower on
+// narrow weights although W then streamed from DRAM only once.
 constexpr int RL_GROUP_BUDGET_MB = 40;
-constexpr int RL_GROUP_MAX = 10;
+constexpr int RL_GROUP_MAX = 16;
 int pick_group_m(int m_tiles, long long row_tile_bytes) {
   long long g = ((long long)RL_GROUP_BUDGET_MB << 20) / (row_tile_bytes > 0 ? row_tile_bytes : 1);
   if (g > RL_GROUP_MAX) g = RL_GROUP_MAX;
