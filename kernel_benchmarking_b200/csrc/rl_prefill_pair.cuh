@@ -593,7 +593,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             for (int j = 0; j < 16; ++j) {
               const float g0 = __uint_as_float(vg[2 * j]) * r, g1 = __uint_as_float(vg[2 * j + 1]) * r;
               const float u0 = __uint_as_float(vu[2 * j]) * r, u1 = __uint_as_float(vu[2 * j + 1]) * r;
-              o[j] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+              // silu(g) = g / (1 + e^-g) with the fast exponential and division: the result is rounded to bf16
+              // (8 bits of mantissa) right after, and an IEEE division per output would dominate this epilogue
+              o[j] = pack_bf16x2(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
             }
           }
           if (c == 1) {
