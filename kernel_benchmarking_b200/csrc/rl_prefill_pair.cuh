@@ -4,20 +4,25 @@
 // its own halves - x rows [128 x 64] and W rows [BN/2 x 64] per k-block, no multicast - and
 // the pair's MMA (M = 256, N = BN, issued by one lane of the rank-0 CTA) reads both W halves
 // from the two CTAs' shared memory, so every byte brought in from L2 feeds twice the math of
-// a single-CTA tile.
+// a single-CTA tile.  (Elements per k-block: 64 bf16, or 128 e4m3 in the FP8 configuration -
+// 128 bytes per tile row either way.)
 //
 // A_TS_FOLD: the gamma-folded activation tile is the MMA's A operand in tensor memory.  The
-//   transform warps read the landed x tile from shared memory, accumulate each row's sum of
-//   squares, multiply by gamma and tcgen05.st the result into a ring of ASLOTS A slots that
-//   sits behind the accumulators.
-// A_SS_DIRECT (gamma == nullptr, the reference operator): the MMA reads x straight from
-//   shared memory; the transform warps only accumulate the sums of squares.
+//   transform warps read the landed x tile from shared memory, multiply by gamma (and, without
+//   the row-statistics pre-pass, accumulate each row's sum of squares) and tcgen05.st the
+//   result into a ring of ASLOTS A slots that sits behind the accumulators.
+// A_SS_DIRECT (gamma == nullptr - the reference operator -, the plain GEMM, LoRA, FP8): the MMA
+//   reads x straight from shared memory.  With 1/rms from the pre-pass (PRESTATS) there is no
+//   transform stage at all: TG = 0, the CTA is producer + MMA issuer + four epilogue warps, and the
+//   x tile completes on the same barrier as the W tile.  Without the pre-pass the transform warps
+//   accumulate the sums of squares.
 // TMEM per CTA: NACC accumulators of BN columns, then ASLOTS x 32 columns of A ring.
 //
 // Barriers (shared memory, identical offsets in both CTAs):
 //   fullA[s]    local        x tile + gamma slice landed              producer -> own transform warps
 //   ready[s]    rank 0 only  both W halves landed (2 arrivals + tx) and both CTAs' transform warps
 //                            done with slot s (8 arrivals): the one wait per k-block of the MMA loop
+//                            (no transform stage: 2 arrivals + the tx of both x and both W halves)
 //   empty[s]    local        MMAs that read slot s are done            MMA commit (multicast) -> producers,
 //                                                                      and -> transform warps (A slot reuse)
 //   tfull[a]    local        accumulator a complete                    MMA commit (multicast) -> epilogues
