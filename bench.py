@@ -193,18 +193,26 @@ def shard_range(N, world, rank):
     return shard_bounds(N, world, rank, multiple=256)
 
 
-def make_buffers(M, N, K, dev, sets, seed, fp8=False):
-    """`sets` independent (x, gamma, W, y, w_scale) groups, generated on the device from a seeded generator, so
-    that consecutive steps never find their inputs in L2."""
-    g = torch.Generator(device=dev).manual_seed(seed)
+W_CHUNK = 256   # weight rows generated per seeded chunk (shards are multiples of it)
+
+
+def make_buffers(M, n0, n1, K, dev, sets, seed, fp8=False):
+    """`sets` independent (x, gamma, W, y, w_scale) groups, generated on the device, so that consecutive steps never
+    find their inputs in L2.  x and gamma depend only on (seed, set): every rank holds the same ones (x is
+    replicated).  W is rows [n0, n1) of one layer whose rows are generated chunk by chunk from (seed, set, chunk):
+    whatever the sharding, the ranks hold slices of the same weight matrix."""
     out = []
-    for _ in range(sets):
+    N = n1 - n0
+    for s in range(sets):
+        g = torch.Generator(device=dev).manual_seed(seed + 7919 * s)
         x = torch.randn(M, K, generator=g, dtype=torch.float32, device=dev).to(torch.bfloat16)
         gamma = (1.0 + 0.1 * torch.randn(K, generator=g, dtype=torch.float32, device=dev)).to(torch.bfloat16)
         W = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
-        for n0 in range(0, N, 8192):       # slabs bound the fp32 temporaries
-            n1 = min(N, n0 + 8192)
-            W[n0:n1] = (torch.randn(n1 - n0, K, generator=g, dtype=torch.float32, device=dev) * K ** -0.5).to(torch.bfloat16)
+        for c0 in range(n0 - n0 % W_CHUNK, n1, W_CHUNK):
+            gw = torch.Generator(device=dev).manual_seed((seed + 7919 * s) * 100003 + c0 // W_CHUNK + 1)
+            chunk = (torch.randn(W_CHUNK, K, generator=gw, dtype=torch.float32, device=dev) * K ** -0.5).to(torch.bfloat16)
+            lo, hi = max(c0, n0), min(c0 + W_CHUNK, n1)
+            W[lo - n0:hi - n0] = chunk[lo - c0:hi - c0]
         wsc = None
         if fp8:
             # per-output-channel absmax / 448 scales, weights stored as e4m3 codes
@@ -332,8 +340,8 @@ class Runner:
         self.flops = 2.0 * self.M * self.N * self.K                    # this rank's share
         self.flops_total = 2.0 * self.M * self.N_total * self.K
         self.sets = max(2, -(-2 * L2_BYTES // self.step_bytes))        # rotate enough buffer sets to exceed 2x L2
-        self.bufs = make_buffers(self.M, (2 if self.op == "swiglu" else 1) * self.N, self.K, dev, self.sets,
-                                 seed=18 + 1000 * rank, fp8=self.fp8)
+        w0, w1 = (n0, n1) if self.op != "swiglu" else (0, 2 * self.N)
+        self.bufs = make_buffers(self.M, w0, w1, self.K, dev, self.sets, seed=18, fp8=self.fp8)
         if self.op == "swiglu":      # W is [2N, K] (gate rows, then up rows), y [M, N]
             self.bufs = [(x, g, W, y[:, : self.N].contiguous(), w) for (x, g, W, y, w) in self.bufs]
         if self.op == "lora":

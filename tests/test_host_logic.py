@@ -197,3 +197,24 @@ def test_clock_summary_picks_the_samples_under_load():
     out = bench.summarize_clock_samples([idle] * 4 + lag)
     assert out["sm_mhz"] == 1490.0 and out["loaded_by"].startswith("power")
     assert bench.summarize_clock_samples([])["sm_mhz"] is None
+
+
+def test_bench_ranks_hold_slices_of_one_layer():
+    """bench.py's synthetic layer: every rank generates the same x and gamma, and its rows of W are a slice of one
+    weight matrix whatever the sharding."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    dev = torch.device("cpu")
+    full = bench.make_buffers(8, 0, 1024, 64, dev, 2, seed=18)
+    parts = [bench.make_buffers(8, a, b, 64, dev, 2, seed=18) for a, b in ((0, 512), (512, 1024), (768, 1024))]
+    for s in range(2):
+        for part, (a, b) in zip(parts, ((0, 512), (512, 1024), (768, 1024))):
+            assert torch.equal(part[s][0], full[s][0]) and torch.equal(part[s][1], full[s][1])     # x, gamma replicated
+            assert torch.equal(part[s][2], full[s][2][a:b])                                          # W rows [a, b)
+    assert not torch.equal(full[0][2], full[1][2])       # the rotating buffer sets differ
+    x, gm, Wq, y, wsc = bench.make_buffers(8, 256, 768, 64, dev, 1, seed=18, fp8=True)[0]
+    assert Wq.dtype == torch.float8_e4m3fn and wsc.shape == (512,) and y.shape == (8, 512)
+    assert bench.dram_traffic("prefill_pair_prestats", 16384, 57344, 8192)[0] == 8 * bench.dram_traffic("prefill_pair_prestats", 16384, 7168, 8192)[0]
+    assert bench.dram_traffic("decode", 3, 28672, 4096)[0] is None
