@@ -119,7 +119,11 @@ class ExperimentRow:
     def measure(self, kernel: Callable, tensors: Sequence, ref: torch.Tensor, ncu: bool = False) -> None:
         stream = getattr(kernel, "_stream", None) or torch.cuda.current_stream()
         with torch.cuda.stream(stream):
-            out = kernel(*tensors)
+            torch.cuda.nvtx.range_push(self.label)     # lets a profiler pick this row's launches by name (--nvtx-include)
+            try:
+                out = kernel(*tensors)
+            finally:
+                torch.cuda.nvtx.range_pop()
             if ncu:            # one launch, nothing else: the profiler wraps the process
                 torch.cuda.synchronize()
                 return
