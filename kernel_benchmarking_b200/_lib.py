@@ -39,6 +39,7 @@ VARIANTS = {
     "prefill_pair_prestats": 14,
     "prefill_pair_prestats_whole": 15,
     "prefill_pair_direct_prestats": 16,
+    "prefill_pair_prescaled": 17,
     "decode": 20,
     "auto_whole": 30,
 }

@@ -138,21 +138,35 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 constexpr size_t TAIL_SLOT_BYTES = (size_t)128 * 256 * 4;
 constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
 
+// Layers at least this wide fold gamma into a copy of x once, in the row-statistics pre-pass, instead of in every
+// column tile's main loop (rowscale_kernel): the fold is then done once per activation, not N / 256 times, and the
+// GEMM runs without transform warps and with two accumulators.  The copy costs one more pass over x that the GEMM
+// has to wait for (4 M K bytes of DRAM traffic), whatever N.  Measured, gamma folded in the main loop against in
+// the pre-pass, same bits out: N = 1536 5 % slower, 4096 equal, 6144 2 % faster, 8192 to 28672 4-6 % faster
+// (bursts and seconds-long loops alike).
+constexpr int RL_PRESCALE_MIN_N = 6144;
+
 struct WsLayout {
   size_t counters_off, ssq_off, partials_off, total;
   size_t rstd_off, tail_off, min_total;  // M > 64 only
+  size_t tail_total;                     // M > 64: end of the k-split partial blocks
+  size_t xs_off, xs_bytes;               // M > 64, wide layers: the gamma-folded copy of x [M, K] (0 bytes otherwise)
 };
-WsLayout ws_layout(int M, int N) {
+WsLayout ws_layout(int M, int N, int K = 0) {
   WsLayout w{};
   if (M > 64) {
     // status block, the counter region every shape keeps at the same place (zero between launches), 1/rms per
-    // token for the PRESTATS kernels, then the partial blocks of k-split tail tiles.  A workspace that ends
-    // before the partial blocks (min_total) still works: the tail tiles are then computed whole.
+    // token for the PRESTATS kernels, the partial blocks of k-split tail tiles, then (wide layers) the folded copy
+    // of x.  A workspace that ends before the partial blocks (min_total) still works: the tail tiles are then
+    // computed whole; one that ends before the copy (tail_total) still works: gamma is folded in the main loop.
     w.counters_off = STATUS_BYTES;
     w.rstd_off = STATUS_BYTES + COUNTER_BYTES;
     w.tail_off = w.rstd_off + align_up((size_t)M * 4, 256);
     w.min_total = w.tail_off;
-    w.total = w.tail_off + TAIL_BYTES;
+    w.tail_total = w.tail_off + TAIL_BYTES;
+    w.xs_off = w.tail_total;
+    w.xs_bytes = (N >= RL_PRESCALE_MIN_N && K > 0) ? align_up((size_t)M * (size_t)K * 2, 256) : 0;
+    w.total = w.xs_off + w.xs_bytes;
     return w;
   }
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -276,6 +290,7 @@ struct PairArgs {
   size_t ws_bytes = 0;
   size_t tail_off = 0, ws_total = 0;   // where the partial blocks of k-split tiles live, and the size that holds them
   int sms = 0;
+  void* xs = nullptr;                  // gamma-folded copy of x [M, K] for the pre-pass to write (wide layers), or nullptr
   cudaStream_t st = nullptr;
   bool no_norm = false;                // plain GEMM: no row statistics at all
   bool split_tail = true;
@@ -294,11 +309,16 @@ int launch_prefill_pair(const PairArgs& a) {
   const int M = a.M, N = a.N, K = a.K;
   const CUtensorMapDataType dt = Cfg::FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int eb = Cfg::FP8 ? 1 : 2;
-  if ((rc = make_map(&tx, dt, eb, a.x, K, M, a.ldx, Cfg::KBW, 128))) return rc;
+  // gamma folded by the pre-pass into a dense copy of x: the GEMM reads the copy and sees no gamma
+  const bool prescale = (a.xs != nullptr);
+  if (prescale && !(Cfg::AMODE == A_SS_DIRECT && Cfg::PRESTATS && !Cfg::FP8 && !Cfg::SWIGLU && a.gamma != nullptr &&
+                    !a.no_norm && a.x2 == nullptr))
+    return RL_ERR_BAD_VARIANT;
+  if ((rc = make_map(&tx, dt, eb, prescale ? a.xs : a.x, K, M, prescale ? (int64_t)K : a.ldx, Cfg::KBW, 128))) return rc;
   if ((rc = make_map(&tw, dt, eb, a.W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, a.ldw, Cfg::KBW, Cfg::BN / 2)))
     return rc;
   if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, N, M, a.ldy, 64, 128))) return rc;
-  if (Cfg::AMODE == A_SS_DIRECT && a.gamma != nullptr) return RL_ERR_BAD_VARIANT;
+  if (Cfg::AMODE == A_SS_DIRECT && a.gamma != nullptr && !prescale) return RL_ERR_BAD_VARIANT;
   tx2 = tx;
   tw2 = tw;
   if (a.x2 != nullptr) {
@@ -309,7 +329,8 @@ int launch_prefill_pair(const PairArgs& a) {
   }
   PrefillParams p{};
   p.M = M; p.N = N; p.K = K; p.eps = a.eps;
-  p.gamma = a.gamma;
+  p.gamma = prescale ? nullptr : a.gamma;
+  p.x_from_prepass = prescale ? 1 : 0;
   p.m_tiles = (M + 255) / 256;
   p.n_tiles = Cfg::SWIGLU ? (N + 127) / 128 : (N + Cfg::BN - 1) / Cfg::BN;  // SwiGLU: N = output channels, W has 2N rows
   p.group_m = pick_group_m(p.m_tiles, (long long)256 * K * eb);
@@ -322,7 +343,11 @@ int launch_prefill_pair(const PairArgs& a) {
   } else if (Cfg::PRESTATS && !a.no_norm) {
     if (a.status == nullptr) return RL_ERR_WORKSPACE;
     float* rstd = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.status) + ws_layout(M > 65 ? M : 65, N).rstd_off);
-    rowstats_kernel<<<(M + 3) / 4, 128, 0, a.st>>>(reinterpret_cast<const __nv_bfloat16*>(a.x), rstd, M, K, a.ldx, a.eps);
+    if (prescale)
+      rowscale_kernel<<<(M + 3) / 4, 128, 0, a.st>>>(reinterpret_cast<const __nv_bfloat16*>(a.x), a.gamma,
+                                                     reinterpret_cast<__nv_bfloat16*>(a.xs), rstd, M, K, a.ldx, K, a.eps);
+    else
+      rowstats_kernel<<<(M + 3) / 4, 128, 0, a.st>>>(reinterpret_cast<const __nv_bfloat16*>(a.x), rstd, M, K, a.ldx, a.eps);
     p.row_rstd = rstd;
   }
   cudaError_t e = set_smem_once(prefill_pair_kernel<Cfg>, Cfg::SMEM_BYTES);
@@ -505,7 +530,7 @@ int static_scratch_address(uint8_t** out) {
 }
 
 // What RL_VARIANT_AUTO runs for a bf16 call.
-int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms) {
+int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms, bool ws_holds_copy = false) {
   if (M <= 64) return RL_VARIANT_DECODE;
   // 64 < M <= 128 runs on the CTA-pair kernel as well (half of each 256-row tile is padding, but the tiles can be
   // cut along K over all pairs: measured 20-30 % faster than one CTA per 128 x 192 tile, which leaves SMs idle)
@@ -521,6 +546,8 @@ int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms) {
   const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
   const bool one_round = tiles <= pairs && 2 * tiles > pairs;
   if (!has_workspace || one_round) return has_gamma ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_PAIR_DIRECT;
+  // wide layers: gamma folded once per activation by the pre-pass instead of once per column tile in the main loop
+  if (has_gamma && ws_holds_copy && N >= RL_PRESCALE_MIN_N) return RL_VARIANT_PREFILL_PAIR_PRESCALED;
   return has_gamma ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
 }
 
@@ -554,7 +581,7 @@ const char* rl_error_string(int code) {
 size_t rl_workspace_bytes(int M, int N, int K, int w_dtype) {
   if (M <= 0 || N <= 0 || K <= 0) return STATUS_BYTES;
   if (w_dtype == RL_W_E4M3) return fp8_ws_layout(M, K).total;
-  return ws_layout(M, N).total;
+  return ws_layout(M, N, K).total;
 }
 
 int rl_plan_tail_split(int M, int N, int K, int pairs, int* tail_tiles, int* split) {
@@ -572,7 +599,7 @@ int rl_select_variant(int M, int N, int K, int has_gamma, int has_workspace) {
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms);
+  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms, has_workspace != 0);
 }
 
 int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -594,7 +621,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   const bool decode = (variant == RL_VARIANT_DECODE) || (variant == RL_VARIANT_AUTO && M <= 64);
   if (decode && M > 64) return RL_ERR_BAD_VARIANT;
   if (!decode && ((ldy & 7) || !aligned16(y))) return RL_ERR_ALIGNMENT;
-  const WsLayout wl = ws_layout(decode || M > 65 ? M : 65, N);
+  const WsLayout wl = ws_layout(decode || M > 65 ? M : 65, N, K);
   if (decode && !workspace) return RL_ERR_WORKSPACE;
   if (workspace && workspace_bytes < (decode ? wl.total : wl.min_total)) return RL_ERR_WORKSPACE;
   DeviceInfo di;
@@ -613,12 +640,13 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
   }
 
   // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
-  if (variant == RL_VARIANT_AUTO) variant = select_variant(M, N, g != nullptr, workspace != nullptr, di.sms);
+  const bool ws_holds_copy = workspace != nullptr && wl.xs_bytes > 0 && workspace_bytes >= wl.total;
+  if (variant == RL_VARIANT_AUTO) variant = select_variant(M, N, g != nullptr, workspace != nullptr, di.sms, ws_holds_copy);
   const bool split_tail = !auto_whole && (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
   PairArgs pa;
   pa.x = x; pa.gamma = g; pa.W = W; pa.y = y;
   pa.M = M; pa.N = N; pa.K = K; pa.ldx = ldx; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;
-  pa.status = status; pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
+  pa.status = status; pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.tail_total;
   pa.sms = di.sms; pa.st = st; pa.split_tail = split_tail;
 #define RL_PREFILL(BN, ST, AM, TG) \
   launch_prefill<PrefillCfg<BN, ST, AM, TG>>(x, g, W, y, M, N, K, ldx, ldw, ldy, eps, status, di.sms, st)
@@ -634,6 +662,14 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_PAIR_PRESTATS:
     case RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE: return launch_prefill_pair<PairFold>(pa);
     case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return launch_prefill_pair<PairDirect>(pa);
+    case RL_VARIANT_PREFILL_PAIR_PRESCALED: {
+      // any width when asked for by name; the workspace must hold the copy (rl_workspace_bytes sizes it for wide layers only)
+      if (g == nullptr || workspace == nullptr) return RL_ERR_BAD_VARIANT;
+      const size_t copy_bytes = align_up((size_t)M * (size_t)K * 2, 256);
+      if (workspace_bytes < wl.xs_off + copy_bytes) return RL_ERR_WORKSPACE;
+      pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
+      return launch_prefill_pair<PairDirect>(pa);
+    }
     default: return RL_ERR_BAD_VARIANT;
   }
 #undef RL_PREFILL

@@ -37,6 +37,7 @@ struct PrefillParams {
   unsigned* tail_counters;
   float* tail_partials;
   int extra_kb;  // pair kernels: k-blocks appended from a second pair of operand matrices (0 or 1)
+  int x_from_prepass;  // pair kernels: the activation matrix is written by the kernel launched just before (rowscale_kernel)
 };
 
 // Row statistics on their own: rstd[m] = rsqrt(mean_k x[m,k]^2 + eps).  One warp per token row, 16-byte
@@ -71,6 +72,47 @@ __global__ void __launch_bounds__(128) rowstats_kernel(const __nv_bfloat16* __re
     ffma2_sq(acc, bf16lo(u.z), bf16hi(u.z));
     ffma2_sq(acc, bf16lo(u.w), bf16hi(u.w));
   }
+  float s = acc.x + acc.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) rstd[m] = 1.0f / sqrtf(s / (float)K + eps);
+}
+
+// Row statistics and the gamma fold in one pass over x: rstd[m] as above and xs[m, k] = bf16(x[m, k] * gamma[k]), the
+// product rounded once to bf16 exactly as the GEMM kernels' transform warps round it.  For wide layers: each
+// activation is then folded once here instead of once per 256-channel column tile in the main loop, and the GEMM
+// runs without transform warps (x straight from shared memory, two accumulators).  One warp per token row.
+__global__ void __launch_bounds__(128) rowscale_kernel(const __nv_bfloat16* __restrict__ x,
+                                                       const __nv_bfloat16* __restrict__ gamma,
+                                                       __nv_bfloat16* __restrict__ xs, float* __restrict__ rstd, int M,
+                                                       int K, long long ldx, long long ldxs, float eps) {
+  launch_dependents();  // the GEMM behind this kernel sets itself up meanwhile; it waits before its first load
+  const int m = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)m * ldx);
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  uint4* out = reinterpret_cast<uint4*>(xs + (size_t)m * ldxs);
+  const int chunks = K >> 3;
+  float2 acc = make_float2(0.f, 0.f);
+  auto one = [&](const uint4 u, const uint4 g, int c) {
+    ffma2_sq(acc, bf16lo(u.x), bf16hi(u.x));
+    ffma2_sq(acc, bf16lo(u.y), bf16hi(u.y));
+    ffma2_sq(acc, bf16lo(u.z), bf16hi(u.z));
+    ffma2_sq(acc, bf16lo(u.w), bf16hi(u.w));
+    out[c] = make_uint4(mul_bf16x2(u.x, g.x), mul_bf16x2(u.y, g.y), mul_bf16x2(u.z, g.z), mul_bf16x2(u.w, g.w));
+  };
+  int c = lane;
+  for (; c + 96 < chunks; c += 128) {  // four independent 16-byte loads of x (and of gamma, from L1) in flight per lane
+    uint4 u[4], g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) u[i] = xr[c + 32 * i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) g[i] = __ldg(gr + c + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) one(u[i], g[i], c + 32 * i);
+  }
+  for (; c < chunks; c += 32) one(xr[c], __ldg(gr + c), c);
   float s = acc.x + acc.y;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);

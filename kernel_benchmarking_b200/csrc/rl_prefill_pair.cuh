@@ -205,8 +205,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     bool ok = true;
     const uint32_t lead_ready0 = mapa_shared(bar_ready(0), 0);
     PairItem w;
-    // FP8: the quantised activations are written by the kernel launched just before this one
-    if (FP8) grid_dependency_wait();
+    // FP8, or gamma folded by the pre-pass: the activations are written by the kernel launched just before this one
+    if (FP8 || p.x_from_prepass) grid_dependency_wait();
     for (int i = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i, w); ++i) {
       int mt, nt;
       prefill_tile_coords(w.t, p, mt, nt);

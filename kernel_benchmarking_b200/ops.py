@@ -134,7 +134,10 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
         _lib.check(rc, "rl_rmsnorm_linear_fp8w")
         return out
     with _on_device(x.device):
-        ws = _workspace(x.device, lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16), stream)
+        nbytes = lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16)
+        if v == _lib.VARIANTS["prefill_pair_prescaled"]:
+            nbytes += M * K * 2 + 256  # room for the gamma-folded copy of x at widths where AUTO would not make one
+        ws = _workspace(x.device, nbytes, stream)
         rc = lib.rl_rmsnorm_linear_bf16(
             x.data_ptr(), None if gamma is None else gamma.data_ptr(), W.data_ptr(), out.data_ptr(),
             M, N, K, x.stride(0), W.stride(0), out.stride(0), ctypes.c_float(eps),

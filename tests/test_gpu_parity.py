@@ -66,7 +66,7 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
                                      "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
                                      "prefill_pair_direct", "prefill_pair_prestats", "prefill_pair_direct_prestats",
-                                     "prefill_pair_prestats_whole"])
+                                     "prefill_pair_prestats_whole", "prefill_pair_prescaled"])
 @pytest.mark.parametrize("has_gamma", [False, True])
 @pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
 def test_every_prefill_variant(variant, has_gamma, M, N, K):
@@ -74,6 +74,11 @@ def test_every_prefill_variant(variant, has_gamma, M, N, K):
         with pytest.raises(ValueError):   # those variants read x straight from shared memory: no gamma fold
             x, gm, W = orc.make_inputs(256, 256, 64, gamma=True)
             kb.rmsnorm_linear(x.to(DEV), gm.to(DEV), W.to(DEV), 1e-6, variant=variant)
+        return
+    if variant == "prefill_pair_prescaled" and not has_gamma:
+        with pytest.raises(ValueError):   # the pre-pass folds gamma into a copy of x: nothing to do without one
+            x, _, W = orc.make_inputs(256, 256, 64, gamma=False)
+            kb.rmsnorm_linear(x.to(DEV), None, W.to(DEV), 1e-6, variant=variant)
         return
     x, gm, W = orc.make_inputs(M, N, K, seed=11, gamma=has_gamma)
     ref = orc.reference_fp32(x, gm, W, 1e-6)
@@ -638,6 +643,57 @@ def test_status_check_clears_the_workspace_after_a_timeout():
     assert orc.rel_max_err(run(x, gm, W, 1e-6), ref) <= BF16_TOL
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 520, 328), (1100, 2048, 1024), (512, 6144, 256), (2048, 8192, 512)])
+def test_gamma_folded_by_the_pre_pass_gives_the_bits_of_the_main_loop_fold(M, N, K):
+    """Wide layers fold gamma once per activation in the row-statistics pre-pass (a copy of x in the workspace)
+    instead of once per column tile in the GEMM's main loop: the product is rounded to bf16 the same way and the
+    MMAs add in the same order, so the two give the same bits."""
+    x, gm, W = orc.make_inputs(M, N, K, seed=21)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y_pre = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_prescaled")
+    y_loop = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_prestats")
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert torch.equal(y_pre, y_loop)
+    assert orc.rel_max_err(y_pre.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+    # x as a column slice of a wider buffer: the copy is dense whatever the caller's leading dimension
+    xb = torch.zeros(M, K + 72, dtype=torch.bfloat16, device=DEV)
+    xb[:, :K] = xd
+    assert torch.equal(kb.rmsnorm_linear(xb[:, :K], gd, Wd, 1e-6, variant="prefill_pair_prescaled"), y_pre)
+    kb.check_status()
+
+
+def test_auto_folds_gamma_in_the_pre_pass_only_when_the_workspace_holds_the_copy():
+    import ctypes
+    lib = _lib.load()
+    M, N, K = 1024, 6144, 256                    # 96 tiles: more than one round of the 74 CTA pairs
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N, K, 1, 1)] == "prefill_pair_prescaled"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N - 256, K, 1, 1)] == "prefill_pair_prestats"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N, K, 0, 1)] == "prefill_pair_direct_prestats"
+    full = lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16)
+    narrow = lib.rl_workspace_bytes(M, N - 256, K, _lib.RL_W_BF16)
+    assert full >= narrow + M * K * 2            # the copy is counted for wide layers only
+    x, gm, W = orc.make_inputs(M, N, K, seed=22)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y_auto = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    # the same call through the C ABI with a workspace that ends before the copy: still runs (gamma folded in the
+    # main loop) and, the two forms being bit-identical, gives the same result
+    ws = torch.zeros(narrow, dtype=torch.uint8, device=DEV)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.rl_rmsnorm_linear_bf16(xd.data_ptr(), gd.data_ptr(), Wd.data_ptr(), y.data_ptr(), M, N, K, K, K, N,
+                                    ctypes.c_float(1e-6), ws.data_ptr(), ws.numel(), 0, st)
+    assert rc == 0
+    # asked for by name with that workspace: refused, nothing launched
+    rc = lib.rl_rmsnorm_linear_bf16(xd.data_ptr(), gd.data_ptr(), Wd.data_ptr(), y.data_ptr(), M, N, K, K, K, N,
+                                    ctypes.c_float(1e-6), ws.data_ptr(), ws.numel(),
+                                    _lib.VARIANTS["prefill_pair_prescaled"], st)
+    assert rc == _lib.RL_ERR_WORKSPACE
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_auto)
+    assert orc.rel_max_err(y.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+
+
 def test_auto_whole_never_splits_and_matches():
     """`variant="auto_whole"`: the kernels AUTO picks, every tile computed whole (no CTA waits for another)."""
     for (M, N, K, has_gamma) in [(4096, 1536, 7168, True), (512, 1024, 4096, False), (8, 1024, 512, True)]:
@@ -647,7 +703,8 @@ def test_auto_whole_never_splits_and_matches():
         assert orc.rel_max_err(yw, orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
         assert orc.rel_max_err(yw, ya.float()) <= ONE_ULP
     lib = _lib.load()
-    assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 1, 1)] == "prefill_pair_prestats"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 1, 1)] == "prefill_pair_prescaled"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 4096, 4096, 1, 1)] == "prefill_pair_prestats"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(4096, 6144, 4096, 0, 1)] == "prefill_pair_direct_prestats"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(16, 28672, 4096, 1, 1)] == "decode"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(100, 512, 512, 1, 1)] == "prefill_pair_prestats"
