@@ -70,7 +70,12 @@ EXTRA_MULTI = ["fp8w_8192x14336x4096"]
 # DRAM bytes (read + written) per launch of the dominant kernel, from one profiler capture each, keyed by the
 # kernel variant and the per-GPU shape it was captured on.  A run whose variant or shape is not listed reports null.
 MEASURED_DRAM_BYTES = {
-    ("prefill_pair_prestats", 4096, 6144, 4096): 128.0e6,
+    # the GEMM kernel on the gamma-folded copy of x; the pre-pass that writes the copy adds up to 4 M K bytes
+    ("prefill_pair_prescaled", 4096, 6144, 4096): 125.6e6,
+    ("prefill_pair_prescaled", 16384, 7168, 8192): 2332.6e6,
+    ("prefill_pair_prescaled", 16384, 14336, 8192): 4895.8e6,
+    # gamma folded in the main loop (by name on these shapes; AUTO runs it for N < 6144)
+    ("prefill_pair_prestats", 4096, 6144, 4096): 130.4e6,
     ("prefill_pair_prestats", 16384, 7168, 8192): 2230.5e6,
     ("prefill_pair_prestats", 16384, 14336, 8192): 4638.0e6,
     ("e4m3 pair kernel", 8192, 14336, 4096): 354.0e6,       # the GEMM kernel; the quantisation pre-pass adds 74 MB
@@ -80,9 +85,10 @@ MEASURED_DRAM_BYTES = {
     ("e4m3 decode", 16, 28672, 4096): 122.0e6,
 }
 # The default workload's launches (3.1 GB on the device at N = 1) are too large to capture.  The two captures of its
-# column shards above show its traffic growing in proportion to the weight rows (x 2.08 for twice the rows), so a
+# column shards above show its traffic growing in proportion to the weight rows (x 2.10 for twice the rows), so a
 # shard of N rows is given the 7168-row capture's bytes times N / 7168, and the line says that it is scaled.
-SCALED_FROM = ("prefill_pair_prestats", 16384, 7168, 8192)
+SCALED_FROM = {"prefill_pair_prescaled": ("prefill_pair_prescaled", 16384, 7168, 8192),
+               "prefill_pair_prestats": ("prefill_pair_prestats", 16384, 7168, 8192)}
 
 
 def dram_traffic(kernel, M, N, K):
@@ -90,11 +96,15 @@ def dram_traffic(kernel, M, N, K):
     v = MEASURED_DRAM_BYTES.get((kernel, M, N, K))
     if v is not None:
         return v, "one ncu capture of this kernel at this shape"
-    k0, m0, n0, kk0 = SCALED_FROM
-    if (kernel, M, K) == (k0, m0, kk0) and N % 256 == 0 and N > n0:
-        return MEASURED_DRAM_BYTES[SCALED_FROM] * N / n0, (f"scaled by N / {n0} from an ncu capture of {m0}x{n0}x{kk0} "
-                                                             "(measured proportional to the weight rows)")
+    base = SCALED_FROM.get(kernel)
+    if base is not None:
+        _, m0, n0, kk0 = base
+        if (M, K) == (m0, kk0) and N % 256 == 0 and N > n0:
+            return MEASURED_DRAM_BYTES[base] * N / n0, (f"scaled by N / {n0} from an ncu capture of {m0}x{n0}x{kk0} "
+                                                        "(measured proportional to the weight rows)")
     return None, "no capture for this kernel and shape"
+
+
 L2_BYTES = 126 * 1024 * 1024
 WINDOWS = 5
 EPS = 1e-6

@@ -216,5 +216,6 @@ def test_bench_ranks_hold_slices_of_one_layer():
     assert not torch.equal(full[0][2], full[1][2])       # the rotating buffer sets differ
     x, gm, Wq, y, wsc = bench.make_buffers(8, 256, 768, 64, dev, 1, seed=18, fp8=True)[0]
     assert Wq.dtype == torch.float8_e4m3fn and wsc.shape == (512,) and y.shape == (8, 512)
-    assert bench.dram_traffic("prefill_pair_prestats", 16384, 57344, 8192)[0] == 8 * bench.dram_traffic("prefill_pair_prestats", 16384, 7168, 8192)[0]
+    for kernel in ("prefill_pair_prescaled", "prefill_pair_prestats"):
+        assert bench.dram_traffic(kernel, 16384, 57344, 8192)[0] == 8 * bench.dram_traffic(kernel, 16384, 7168, 8192)[0]
     assert bench.dram_traffic("decode", 3, 28672, 4096)[0] is None
