@@ -184,7 +184,9 @@ int rl_rmsnorm_linear_bf16_noalloc(const void* x, const void* gamma, const void*
 /* Fused RMSNorm -> SwiGLU: y[M, N] = silu(h[:, :N]) * h[:, N:] with h = rmsnorm(x) * gamma @ W^T, W [2N, K] =
  * gate rows followed by up rows.  Replaces `rmsnorm_swiglu(a, bb1, eps)`
  * (python/baselines/rmsnorm_swiglu.py:36-42, profiled by demo/new_profiling/swiglu_new.py).  N must be a
- * multiple of 128; needs the workspace of rl_workspace_bytes(max(M, 65), N, K, RL_W_BF16). */
+ * multiple of 128; needs a workspace of rl_workspace_bytes(max(M, 65), 2 * N, K, RL_W_BF16) bytes (the size for a
+ * linear layer with the same 2N weight rows; with no more than rl_workspace_bytes(max(M, 65), N, K, RL_W_BF16)
+ * the call still runs, folding gamma in the main loop). */
 int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void* y, int M, int N, int K,
                            int64_t ldx, int64_t ldw, int64_t ldy, float eps,
                            void* workspace, size_t workspace_bytes, void* stream);

@@ -186,6 +186,7 @@ using PairFoldN192 = PairCfg<192, 2, 6, 4, 2, A_TS_FOLD>;
 using PairDirectFused = PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT>;     // no gamma: x straight from shared memory
 using PairDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true>;    // ... with 1/rms from the pre-pass (or no norm at all)
 using PairSwiglu = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>;
+using PairSwigluDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, true>;  // no gamma, or gamma folded by the pre-pass
 using PairFp8 = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, false, true>;
 
 template <class Cfg>
@@ -311,7 +312,7 @@ int launch_prefill_pair(const PairArgs& a) {
   const int eb = Cfg::FP8 ? 1 : 2;
   // gamma folded by the pre-pass into a dense copy of x: the GEMM reads the copy and sees no gamma
   const bool prescale = (a.xs != nullptr);
-  if (prescale && !(Cfg::AMODE == A_SS_DIRECT && Cfg::PRESTATS && !Cfg::FP8 && !Cfg::SWIGLU && a.gamma != nullptr &&
+  if (prescale && !(Cfg::AMODE == A_SS_DIRECT && Cfg::PRESTATS && !Cfg::FP8 && a.gamma != nullptr &&
                     !a.no_norm && a.x2 == nullptr))
     return RL_ERR_BAD_VARIANT;
   if ((rc = make_map(&tx, dt, eb, prescale ? a.xs : a.x, K, M, prescale ? (int64_t)K : a.ldx, Cfg::KBW, 128))) return rc;
@@ -778,8 +779,9 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7) || (N & 127) || !aligned16(x) || !aligned16(W) || !aligned16(y) ||
       (gamma && !aligned16(gamma)))
     return RL_ERR_ALIGNMENT;
-  const size_t need = ws_layout(65 > M ? 65 : M, N).min_total;
-  if (!workspace || workspace_bytes < need) return RL_ERR_WORKSPACE;
+  // the layout of a linear layer with the same 2N weight rows: wide layers get room for the gamma-folded copy of x
+  const WsLayout wl = ws_layout(65 > M ? 65 : M, 2 * N, K);
+  if (!workspace || workspace_bytes < wl.min_total) return RL_ERR_WORKSPACE;
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
@@ -789,6 +791,13 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
   pa.M = M; pa.N = N; pa.K = K; pa.ldx = ldx; pa.ldw = ldw; pa.ldy = ldy; pa.eps = eps;
   pa.status = reinterpret_cast<int*>(workspace); pa.ws_bytes = workspace_bytes;
   pa.sms = di.sms; pa.st = (cudaStream_t)stream;
+  // without gamma there is nothing to fold: x straight from shared memory.  With gamma the same kernel runs on the
+  // copy the pre-pass folds it into, where the layer is wide enough to pay for the copy and the workspace holds it.
+  if (gamma == nullptr) return launch_prefill_pair<PairSwigluDirect>(pa);
+  if (wl.xs_bytes > 0 && workspace_bytes >= wl.total) {
+    pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
+    return launch_prefill_pair<PairSwigluDirect>(pa);
+  }
   return launch_prefill_pair<PairSwiglu>(pa);
 }
 

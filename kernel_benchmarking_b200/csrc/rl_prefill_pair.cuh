@@ -44,7 +44,7 @@ struct PairCfg {
   // loads gate channels, the rank-1 CTA the matching up channels, so accumulator columns [0,128) and
   // [128,256) hold gate and up of the same 128 output channels and the epilogue emits silu(gate) * up.
   static constexpr bool SWIGLU = SWIGLU_;
-  static_assert(!SWIGLU_ || (BN_ == 256 && NACC_ == 1), "SwiGLU epilogue: 256-column tile, one accumulator");
+  static_assert(!SWIGLU_ || BN_ == 256, "SwiGLU epilogue: 256-column tile (gate and up halves)");
   // FP8: both operands are e4m3 (activations quantised per token by rowquant_kernel, weights with per-channel
   // scales), k-blocks of 128 elements (the same 128 bytes per tile row), kind::f8f6f4 MMAs, and the epilogue
   // multiplies by row_scale[m] * w_scale[n].

@@ -167,7 +167,7 @@ def rmsnorm_swiglu(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
     lib = _lib.load()
     stream = _stream_ptr(x.device)
     with _on_device(x.device):
-        ws = _workspace(x.device, lib.rl_workspace_bytes(max(M, 65), N, K, _lib.RL_W_BF16), stream)
+        ws = _workspace(x.device, lib.rl_workspace_bytes(max(M, 65), 2 * N, K, _lib.RL_W_BF16), stream)
         rc = lib.rl_rmsnorm_swiglu_bf16(x.data_ptr(), None if gamma is None else gamma.data_ptr(), W.data_ptr(),
                                         out.data_ptr(), M, N, K, x.stride(0), W.stride(0), out.stride(0),
                                         ctypes.c_float(eps), ws.data_ptr(), ws.numel(), stream)

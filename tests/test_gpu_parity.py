@@ -522,6 +522,32 @@ def test_swiglu_golden_and_shapes(golden_dir):
         kb.rmsnorm_swiglu(x.to(DEV), gm.to(DEV), W[:200].contiguous().to(DEV), 1e-6)   # n not a multiple of 128
 
 
+def test_swiglu_wide_layers_fold_gamma_in_the_pre_pass():
+    """2n >= 6144 weight rows: gamma is folded into a copy of x by the pre-pass and the GEMM reads x straight from
+    shared memory (as it always does without gamma); with a workspace too small for the copy the fold happens in
+    the main loop.  Same bits either way."""
+    import ctypes
+    lib = _lib.load()
+    M, n, K = 1024, 3072, 512
+    x, gm, W = orc.make_inputs(M, 2 * n, K, seed=31)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y = kb.rmsnorm_swiglu(xd, gd, Wd, 1e-6)
+    y_nogamma = kb.rmsnorm_swiglu(xd, None, Wd, 1e-6)
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert orc.rel_max_err(y.cpu(), orc.torch_rmsnorm_swiglu(x.float(), gm.float(), W.float(), 1e-6)) <= BF16_TOL
+    assert orc.rel_max_err(y_nogamma.cpu(), orc.torch_rmsnorm_swiglu(x.float(), torch.ones(K), W.float(), 1e-6)) <= BF16_TOL
+    small = lib.rl_workspace_bytes(M, n, K, _lib.RL_W_BF16)
+    assert small + M * K * 2 <= lib.rl_workspace_bytes(M, 2 * n, K, _lib.RL_W_BF16)
+    ws = torch.zeros(small, dtype=torch.uint8, device=DEV)
+    y2 = torch.empty(M, n, dtype=torch.bfloat16, device=DEV)
+    rc = lib.rl_rmsnorm_swiglu_bf16(xd.data_ptr(), gd.data_ptr(), Wd.data_ptr(), y2.data_ptr(), M, n, K, K, K, n,
+                                    ctypes.c_float(1e-6), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
+
+
 def test_lora_golden_and_shapes(golden_dir):
     """LoRA-fused linear (the low-rank term as one more k-block of the main loop) against the reference's
     `torch_lora` output and, on larger shapes, against the restatement in fp32 on the GPU."""
