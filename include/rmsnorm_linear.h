@@ -67,8 +67,8 @@ enum {
   RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE = 15, /* as 14, every tile computed whole by one pair */
   RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS = 16, /* gamma == NULL only: 1/rms from the pre-pass, x straight from shared memory, two accumulators */
   RL_VARIANT_PREFILL_PAIR_PRESCALED = 17, /* gamma != NULL: the pre-pass also writes bf16(x * gamma) into the workspace and the GEMM runs as 16
-                                           on that copy; what AUTO runs for N >= 6144 when the workspace holds the copy
-                                           (rl_workspace_bytes counts it for such N); by name for any N, with M * K * 2 + 256
+                                           on that copy; what AUTO runs for N >= 6144 and M * N * K >= 3e10 when the workspace holds the copy
+                                           (rl_workspace_bytes counts it for such shapes); by name for any shape, with M * K * 2 + 256
                                            bytes added to rl_workspace_bytes */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
   RL_VARIANT_DECODE = 20,          /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
@@ -86,7 +86,7 @@ const char* rl_error_string(int code);
 /* Bytes of caller-provided workspace a call with this shape needs (status
  * block; for M <= 64 the split-K partial tiles and tile counters; for M > 64
  * 1/rms per token, the partial blocks of k-split tiles and, with bf16 weights
- * and N >= 6144, M * K * 2 bytes for the gamma-folded copy of x - a call
+ * N >= 6144 and M * N * K >= 3e10, M * K * 2 bytes for the gamma-folded copy of x - a call
  * given less than that still runs, folding gamma in the main loop).  Pure
  * arithmetic, needs no GPU.  No reference counterpart (the reference's kernels
  * allocate through their DSL runtimes). */

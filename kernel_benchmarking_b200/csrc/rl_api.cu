@@ -138,13 +138,19 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 constexpr size_t TAIL_SLOT_BYTES = (size_t)128 * 256 * 4;
 constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
 
-// Layers at least this wide fold gamma into a copy of x once, in the row-statistics pre-pass, instead of in every
-// column tile's main loop (rowscale_kernel): the fold is then done once per activation, not N / 256 times, and the
-// GEMM runs without transform warps and with two accumulators.  The copy costs one more pass over x that the GEMM
-// has to wait for (4 M K bytes of DRAM traffic), whatever N.  Measured, gamma folded in the main loop against in
-// the pre-pass, same bits out: N = 1536 5 % slower, 4096 equal, 6144 2 % faster, 8192 to 28672 4-6 % faster
-// (bursts and seconds-long loops alike).
+// Wide layers fold gamma into a copy of x once, in the row-statistics pre-pass, instead of in every column tile's
+// main loop (rowscale_kernel): the fold is then done once per activation, not N / 256 times, and the GEMM runs
+// without transform warps and with two accumulators.  The copy costs one more pass over x that the GEMM has to
+// wait for (4 M K bytes of DRAM traffic plus a few microseconds of exposed launch and wait), whatever N.  Measured,
+// gamma folded in the main loop against in the pre-pass, same bits out.  By width at M >= 2048: N = 1536 5 %
+// slower, 4096 equal, 6144 2-3 % faster, 8192 to 57344 4-6 % faster (bursts and seconds-long loops alike).  By
+// size at N >= 6144: 128 x 6144 x 4096 and 256 x 8192 x 4096 8-10 % slower (a 30 us GEMM behind a 4 us wait),
+// 512 x 14336 x 4096 and 1024 x 6144 x 4096 equal, 2048 x 8192 x 2048 5 % faster.
 constexpr int RL_PRESCALE_MIN_N = 6144;
+constexpr long long RL_PRESCALE_MIN_MNK = 30000000000ll;   // M N K: a GEMM of about 50 us
+inline bool prescale_pays(int M, int N, int K) {
+  return N >= RL_PRESCALE_MIN_N && (long long)M * N * K >= RL_PRESCALE_MIN_MNK;
+}
 
 struct WsLayout {
   size_t counters_off, ssq_off, partials_off, total;
@@ -165,7 +171,7 @@ WsLayout ws_layout(int M, int N, int K = 0) {
     w.min_total = w.tail_off;
     w.tail_total = w.tail_off + TAIL_BYTES;
     w.xs_off = w.tail_total;
-    w.xs_bytes = (N >= RL_PRESCALE_MIN_N && K > 0) ? align_up((size_t)M * (size_t)K * 2, 256) : 0;
+    w.xs_bytes = (K > 0 && prescale_pays(M, N, K)) ? align_up((size_t)M * (size_t)K * 2, 256) : 0;
     w.total = w.xs_off + w.xs_bytes;
     return w;
   }
@@ -548,7 +554,7 @@ int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms, bo
   const bool one_round = tiles <= pairs && 2 * tiles > pairs;
   if (!has_workspace || one_round) return has_gamma ? RL_VARIANT_PREFILL_PAIR_N256 : RL_VARIANT_PREFILL_PAIR_DIRECT;
   // wide layers: gamma folded once per activation by the pre-pass instead of once per column tile in the main loop
-  if (has_gamma && ws_holds_copy && N >= RL_PRESCALE_MIN_N) return RL_VARIANT_PREFILL_PAIR_PRESCALED;
+  if (has_gamma && ws_holds_copy) return RL_VARIANT_PREFILL_PAIR_PRESCALED;
   return has_gamma ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
 }
 
@@ -600,7 +606,7 @@ int rl_select_variant(int M, int N, int K, int has_gamma, int has_workspace) {
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms, has_workspace != 0);
+  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms, has_workspace != 0 && prescale_pays(M, N, K));
 }
 
 int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {

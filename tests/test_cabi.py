@@ -48,6 +48,8 @@ def test_workspace_bytes_is_pure_arithmetic(lib):
     # layers of 6144 channels and more: room for the gamma-folded copy of x [M, K] as well
     assert lib.rl_workspace_bytes(4096, 6144, 4096, 0) == small + 4096 * 4096 * 2
     assert lib.rl_workspace_bytes(4096, 6144 - 8, 4096, 0) == small
+    # ... and only where the GEMM is long enough for the copy to pay (M N K >= 3e10)
+    assert lib.rl_workspace_bytes(256, 8192, 4096, 0) == small - (4096 - 256) * 4
     w16 = lib.rl_workspace_bytes(16, 28672, 4096, 0)
     w1 = lib.rl_workspace_bytes(1, 28672, 4096, 0)
     w64 = lib.rl_workspace_bytes(64, 28672, 4096, 0)

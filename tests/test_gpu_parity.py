@@ -523,12 +523,12 @@ def test_swiglu_golden_and_shapes(golden_dir):
 
 
 def test_swiglu_wide_layers_fold_gamma_in_the_pre_pass():
-    """2n >= 6144 weight rows: gamma is folded into a copy of x by the pre-pass and the GEMM reads x straight from
+    """2n >= 6144 weight rows (and a GEMM large enough): gamma is folded into a copy of x by the pre-pass and the GEMM reads x straight from
     shared memory (as it always does without gamma); with a workspace too small for the copy the fold happens in
     the main loop.  Same bits either way."""
     import ctypes
     lib = _lib.load()
-    M, n, K = 1024, 3072, 512
+    M, n, K = 2048, 3072, 2560
     x, gm, W = orc.make_inputs(M, 2 * n, K, seed=31)
     xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
     y = kb.rmsnorm_swiglu(xd, gd, Wd, 1e-6)
@@ -692,10 +692,11 @@ def test_gamma_folded_by_the_pre_pass_gives_the_bits_of_the_main_loop_fold(M, N,
 def test_auto_folds_gamma_in_the_pre_pass_only_when_the_workspace_holds_the_copy():
     import ctypes
     lib = _lib.load()
-    M, N, K = 1024, 6144, 256                    # 96 tiles: more than one round of the 74 CTA pairs
+    M, N, K = 2048, 6144, 2560                   # wide enough (N >= 6144) and large enough (M N K >= 3e10) for the copy to pay
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N, K, 1, 1)] == "prefill_pair_prescaled"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N - 256, K, 1, 1)] == "prefill_pair_prestats"
     assert _lib.VARIANT_NAMES[lib.rl_select_variant(M, N, K, 0, 1)] == "prefill_pair_direct_prestats"
+    assert _lib.VARIANT_NAMES[lib.rl_select_variant(256, 8192, 4096, 1, 1)] == "prefill_pair_prestats"   # a 30 us GEMM: no copy
     full = lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16)
     narrow = lib.rl_workspace_bytes(M, N - 256, K, _lib.RL_W_BF16)
     assert full >= narrow + M * K * 2            # the copy is counted for wide layers only
