@@ -11,8 +11,8 @@
 //   transform warps read the landed x tile from shared memory, multiply by gamma (and, without
 //   the row-statistics pre-pass, accumulate each row's sum of squares) and tcgen05.st the
 //   result into a ring of ASLOTS A slots that sits behind the accumulators.
-// A_SS_DIRECT (gamma == nullptr - the reference operator -, the plain GEMM, LoRA, FP8): the MMA
-//   reads x straight from shared memory.  With 1/rms from the pre-pass (PRESTATS) there is no
+// A_SS_DIRECT (gamma == nullptr - the reference operator -, gamma already folded into a copy of x by the
+//   pre-pass, the plain GEMM, LoRA, FP8): the MMA reads x straight from shared memory.  With 1/rms from the pre-pass (PRESTATS) there is no
 //   transform stage at all: TG = 0, the CTA is producer + MMA issuer + four epilogue warps, and the
 //   x tile completes on the same barrier as the W tile.  Without the pre-pass the transform warps
 //   accumulate the sums of squares.
