@@ -376,9 +376,11 @@ int launch_prefill_pair(const PairArgs& a) {
   if (Cfg::PRESTATS && p.row_rstd != nullptr) {
     // behind rowstats_kernel (FP8: rowquant_kernel) with programmatic stream serialisation: the GEMM sets up
     // and, in the bf16 case, streams its tiles while the row statistics are still being computed, and waits only
-    // where it first reads them.  Only in that case: the kernel in front is a normal launch, so everything
-    // earlier in the stream (whoever wrote x and W) is complete before it starts, and the producer warp may load
-    // the caller's operands without waiting.  With the norm switched off nothing is launched in front, and the
+    // where it first reads them.  Only in that case: rowstats_kernel and rowscale_kernel are normal launches, so
+    // everything earlier in the stream (whoever wrote x and W) is complete before they start, and the producer
+    // warp may load the caller's operands without waiting (rowquant_kernel is itself a programmatic dependent that
+    // waits before it reads anything, and the FP8 producer waits for it before its first load, which amounts to
+    // the same).  With the norm switched off nothing is launched in front, and the
     // kernel must not become a programmatic dependent of whatever the caller ran before it: it is launched
     // normally below.
     cudaLaunchConfig_t lc = {};
@@ -484,10 +486,20 @@ int launch_rowquant(const void* x, const void* gamma, void* q, float* row_scale,
   p.q = reinterpret_cast<uint8_t*>(q);
   p.row_scale = row_scale;
   p.M = M; p.K = K; p.ldx = ldx; p.ldq = ldq; p.eps = eps;
-  if (K <= 4096) rowquant_kernel<128><<<M, 128, 0, st>>>(p);
-  else if (K <= 8192) rowquant_kernel<256><<<M, 256, 0, st>>>(p);
-  else rowquant_kernel<512><<<M, 512, 0, st>>>(p);
-  cudaError_t e = cudaGetLastError();
+  // a programmatic dependent of whatever runs in front of it (the kernel waits for that to complete before it
+  // reads anything): 16x28672x4096 with e4m3 weights, steps back to back, 26.8 -> 25.3 us
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3((unsigned)M);
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  cudaError_t e;
+  if (K <= 4096) { lc.blockDim = dim3(128); e = cudaLaunchKernelEx(&lc, rowquant_kernel<128>, p); }
+  else if (K <= 8192) { lc.blockDim = dim3(256); e = cudaLaunchKernelEx(&lc, rowquant_kernel<256>, p); }
+  else { lc.blockDim = dim3(512); e = cudaLaunchKernelEx(&lc, rowquant_kernel<512>, p); }
   return e == cudaSuccess ? RL_OK : cuda_err(e);
 }
 

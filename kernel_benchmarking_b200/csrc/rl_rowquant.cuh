@@ -88,6 +88,10 @@ template <int NT>
 __global__ void __launch_bounds__(NT, 1024 / NT) rowquant_kernel(const RowQuantParams p) {
   __shared__ float2 scratch[NT / 32];
   launch_dependents();  // lets the GEMM behind this kernel run its prologue; it waits before its first load
+  // launched with programmatic stream serialisation itself: behind a kernel that lets its dependents start early
+  // (this library's small-M kernel does) the CTAs are already resident when that kernel ends, which takes this
+  // kernel's launch latency out of a chain of decode steps.  Nothing is read before everything in front is complete.
+  grid_dependency_wait();
   const int m = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx);
   const uint4* gr = reinterpret_cast<const uint4*>(p.gamma);
