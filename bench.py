@@ -367,7 +367,7 @@ class Runner:
             v = _lib.load().rl_select_variant(self.M, self.N, self.K, 1 if gamma else 0, 1)
             self.kernel = _lib.VARIANT_NAMES.get(v, str(v)) if variant == "auto" else str(variant)
         # kernels launched per step: the pre-pass (row statistics / quantisation) and the GEMM, or one fused kernel
-        self.launches_per_step = 2 if (self.fp8 or "prestats" in self.kernel or "prescaled" in self.kernel) else 1
+        self.launches_per_step = 2 if (self.fp8 or any(t in self.kernel for t in ("prestats", "prescaled", "wide"))) else 1
 
     def step(self, i):
         x, g, W, y, wsc = self.bufs[i % self.sets]

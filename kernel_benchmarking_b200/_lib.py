@@ -40,6 +40,7 @@ VARIANTS = {
     "prefill_pair_prestats_whole": 15,
     "prefill_pair_direct_prestats": 16,
     "prefill_pair_prescaled": 17,
+    "prefill_pair_wide": 18,
     "decode": 20,
     "auto_whole": 30,
 }

@@ -148,6 +148,21 @@ constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
 // 512 x 14336 x 4096 and 1024 x 6144 x 4096 equal, 2048 x 8192 x 2048 5 % faster.
 constexpr int RL_PRESCALE_MIN_N = 6144;
 constexpr long long RL_PRESCALE_MIN_MNK = 30000000000ll;   // M N K: a GEMM of about 50 us
+// 256 x 512 tiles (PairWide) halve the activation bytes every pair pulls in and issue eight MMAs per barrier wait
+// instead of four: measured 6-10 % more work per unit of time than 256 x 256 tiles, tile for tile.  Their last round
+// is not cut along K, though, so they run in whole rounds of the resident pairs while the narrow tiles' k-split makes
+// that kernel's time nearly proportional to its tile count.  Wide tiles where the rounds they need, at 93 % of
+// the narrow tiles' time per column, come to less.
+inline bool wide_tiles_pay(int M, int N, int K, int pairs) {
+  if (K < 4096 || pairs <= 0) return false;
+  const long long m_tiles = (M + 255) / 256;
+  const long long tiles512 = m_tiles * ((N + 511) / 512), tiles256 = m_tiles * ((N + 255) / 256);
+  const long long rounds512 = (tiles512 + pairs - 1) / pairs;
+  if (rounds512 < 4) return false;
+  // time in units of one narrow tile: 2 x 0.93 per round of wide tiles; narrow tiles / pairs plus a quarter
+  // for the exchange of the k-split round
+  return 2.0 * 0.93 * (double)rounds512 < (double)tiles256 / pairs + 0.25;
+}
 inline bool prescale_pays(int M, int N, int K) {
   return N >= RL_PRESCALE_MIN_N && (long long)M * N * K >= RL_PRESCALE_MIN_MNK;
 }
@@ -191,6 +206,7 @@ using PairFoldFused = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD>;         // the same w
 using PairFoldN192 = PairCfg<192, 2, 6, 4, 2, A_TS_FOLD>;
 using PairDirectFused = PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT>;     // no gamma: x straight from shared memory
 using PairDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true>;    // ... with 1/rms from the pre-pass (or no norm at all)
+using PairWide = PairCfg<512, 2, 4, 1, 0, A_SS_DIRECT, true>;      // the same on 256 x 512 tiles: half the x bytes per FLOP
 using PairSwiglu = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>;
 using PairSwigluDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, true>;  // no gamma, or gamma folded by the pre-pass
 using PairFp8 = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, false, true>;
@@ -322,7 +338,8 @@ int launch_prefill_pair(const PairArgs& a) {
                     !a.no_norm && a.x2 == nullptr))
     return RL_ERR_BAD_VARIANT;
   if ((rc = make_map(&tx, dt, eb, prescale ? a.xs : a.x, K, M, prescale ? (int64_t)K : a.ldx, Cfg::KBW, 128))) return rc;
-  if ((rc = make_map(&tw, dt, eb, a.W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, a.ldw, Cfg::KBW, Cfg::BN / 2)))
+  if ((rc = make_map(&tw, dt, eb, a.W, K, Cfg::SWIGLU ? 2 * (uint64_t)N : (uint64_t)N, a.ldw, Cfg::KBW,
+                     Cfg::WIDE ? 128 : Cfg::BN / 2)))
     return rc;
   if ((rc = make_map(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, N, M, a.ldy, 64, 128))) return rc;
   if (Cfg::AMODE == A_SS_DIRECT && a.gamma != nullptr && !prescale) return RL_ERR_BAD_VARIANT;
@@ -330,7 +347,7 @@ int launch_prefill_pair(const PairArgs& a) {
   tw2 = tw;
   if (a.x2 != nullptr) {
     // second operand pair [M, L] / [N, L]: same boxes as the first, columns L..63 come back as zeros
-    if (Cfg::AMODE != A_SS_DIRECT || Cfg::SWIGLU || Cfg::FP8 || a.L <= 0 || a.L > 64) return RL_ERR_BAD_VARIANT;
+    if (Cfg::AMODE != A_SS_DIRECT || Cfg::SWIGLU || Cfg::FP8 || Cfg::WIDE || a.L <= 0 || a.L > 64) return RL_ERR_BAD_VARIANT;
     if ((rc = make_map(&tx2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x2, a.L, M, a.ldx2, 64, 128))) return rc;
     if ((rc = make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.w2, a.L, (uint64_t)N, a.ldw2, 64, Cfg::BN / 2))) return rc;
   }
@@ -570,6 +587,15 @@ int select_variant(int M, int N, bool has_gamma, bool has_workspace, int sms, bo
   return has_gamma ? RL_VARIANT_PREFILL_PAIR_PRESTATS : RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS;
 }
 
+// select_variant, then 256 x 512 tiles in place of the transform-free 256 x 256 kernels where those pay.
+int auto_variant(int M, int N, int K, bool has_gamma, bool has_workspace, bool ws_holds_copy, int sms) {
+  const int v = select_variant(M, N, has_gamma, has_workspace, sms, ws_holds_copy);
+  if (v != RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS && v != RL_VARIANT_PREFILL_PAIR_PRESCALED) return v;
+  int pairs = 0;
+  if (max_cta_pairs<PairWide>(sms, &pairs) != RL_OK || !wide_tiles_pay(M, N, K, pairs)) return v;
+  return RL_VARIANT_PREFILL_PAIR_WIDE;
+}
+
 }  // namespace
 
 extern "C" {
@@ -618,7 +644,7 @@ int rl_select_variant(int M, int N, int K, int has_gamma, int has_workspace) {
   int rc = device_info(&di);
   if (rc) return rc;
   if (di.cc_major != 10) return RL_ERR_UNSUPPORTED_ARCH;
-  return select_variant(M, N, has_gamma != 0, has_workspace != 0, di.sms, has_workspace != 0 && prescale_pays(M, N, K));
+  return auto_variant(M, N, K, has_gamma != 0, has_workspace != 0, has_workspace != 0 && prescale_pays(M, N, K), di.sms);
 }
 
 int rl_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -660,7 +686,7 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
 
   // M > 128: CTA pairs on 256 x 256 tiles; a single row-tile of tokens runs on the one-CTA kernel
   const bool ws_holds_copy = workspace != nullptr && wl.xs_bytes > 0 && workspace_bytes >= wl.total;
-  if (variant == RL_VARIANT_AUTO) variant = select_variant(M, N, g != nullptr, workspace != nullptr, di.sms, ws_holds_copy);
+  if (variant == RL_VARIANT_AUTO) variant = auto_variant(M, N, K, g != nullptr, workspace != nullptr, ws_holds_copy, di.sms);
   const bool split_tail = !auto_whole && (variant != RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE);
   PairArgs pa;
   pa.x = x; pa.gamma = g; pa.W = W; pa.y = y;
@@ -681,13 +707,17 @@ int rl_rmsnorm_linear_bf16(const void* x, const void* gamma, const void* W, void
     case RL_VARIANT_PREFILL_PAIR_PRESTATS:
     case RL_VARIANT_PREFILL_PAIR_PRESTATS_WHOLE: return launch_prefill_pair<PairFold>(pa);
     case RL_VARIANT_PREFILL_PAIR_DIRECT_PRESTATS: return launch_prefill_pair<PairDirect>(pa);
+    case RL_VARIANT_PREFILL_PAIR_WIDE:
     case RL_VARIANT_PREFILL_PAIR_PRESCALED: {
       // any width when asked for by name; the workspace must hold the copy (rl_workspace_bytes sizes it for wide layers only)
-      if (g == nullptr || workspace == nullptr) return RL_ERR_BAD_VARIANT;
-      const size_t copy_bytes = align_up((size_t)M * (size_t)K * 2, 256);
-      if (workspace_bytes < wl.xs_off + copy_bytes) return RL_ERR_WORKSPACE;
-      pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
-      return launch_prefill_pair<PairDirect>(pa);
+      const bool by_name_wide = (variant == RL_VARIANT_PREFILL_PAIR_WIDE);
+      if (workspace == nullptr || (g == nullptr && !by_name_wide)) return RL_ERR_BAD_VARIANT;
+      if (g != nullptr) {
+        const size_t copy_bytes = align_up((size_t)M * (size_t)K * 2, 256);
+        if (workspace_bytes < wl.xs_off + copy_bytes) return RL_ERR_WORKSPACE;
+        pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
+      }
+      return by_name_wide ? launch_prefill_pair<PairWide>(pa) : launch_prefill_pair<PairDirect>(pa);
     }
     default: return RL_ERR_BAD_VARIANT;
   }

@@ -50,6 +50,16 @@ struct PairCfg {
   // multiplies by row_scale[m] * w_scale[n].
   static constexpr bool FP8 = FP8_;
   static constexpr int KBW = FP8_ ? 128 : 64;  // elements per k-block
+  // WIDE (BN = 512): one tile is two MMA-wide column halves that share the activation tile - every x byte brought
+  // in from L2 feeds twice the math (the measured upper bound of that saving at the power cap: +7 to +9 %).  The
+  // tile's accumulator is all of tensor memory, so the drain of one tile cannot run under the main loop of the next
+  // as with two 256-column accumulators; the two halves are released separately instead (the barriers that count
+  // accumulators count halves here), and the next tile's first k-block starts on the first half while the second
+  // is still draining.  Each CTA's W stage is two boxes of 128 rows, one per half.
+  static constexpr bool WIDE = (BN_ == 512);
+  static constexpr int MMA_N = WIDE ? 256 : BN_;
+  static_assert(!WIDE || (NACC_ == 2 && AMODE_ == A_SS_DIRECT && PRESTATS_ && !FP8_ && !SWIGLU_),
+                "512-column tiles: transform-free bf16, two separately released halves");
   // XFORM: the kernel has transform warps (they fold gamma and / or accumulate the sums of squares).  Without
   // them (x straight from shared memory, 1/rms from the pre-pass) both operand tiles complete directly on the
   // barrier the MMA warp waits on and the CTA is producer + MMA + epilogue only.
@@ -72,9 +82,10 @@ struct PairCfg {
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64;  // no alignment slack: the kernel checks the base instead
   static constexpr int TMEM_COLS = 512;
-  static constexpr int A_COL0 = NACC * BN;
+  static constexpr int ACC_COLS = WIDE ? BN : NACC * BN;
+  static constexpr int A_COL0 = ACC_COLS;
   static_assert(AMODE == A_TS_FOLD || AMODE == A_SS_DIRECT, "pair kernel: TS fold or SS direct");
-  static_assert(BN % 64 == 0 && BN <= 256, "BN");
+  static_assert(BN % 64 == 0 && (BN <= 256 || BN == 512), "BN");
   static_assert(B_BYTES % 1024 == 0, "W stage alignment");
   static_assert(NACC == 1 || NACC == 2, "NACC");
   // a ring slot is always served by the same transform group (parity waits alias otherwise), and a
@@ -82,7 +93,7 @@ struct PairCfg {
   static_assert(TG == 0 || (STAGES % (TG ? TG : 1) == 0 && (AMODE != A_TS_FOLD || (STAGES - ASLOTS) % (TG ? TG : 1) == 0)),
                 "ring / group layout");
   static_assert(AMODE != A_TS_FOLD || (ASLOTS <= STAGES && NACC * BN + 32 * ASLOTS <= 512), "TMEM budget");
-  static_assert(NACC * BN <= 512, "TMEM budget");
+  static_assert(ACC_COLS <= 512, "TMEM budget");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -125,7 +136,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   constexpr bool TS = (Cfg::AMODE == A_TS_FOLD);
   constexpr bool PRESTATS = Cfg::PRESTATS;
   constexpr bool SWIGLU = Cfg::SWIGLU;
-  constexpr bool FP8 = Cfg::FP8, XFORM = Cfg::XFORM;
+  constexpr bool FP8 = Cfg::FP8, XFORM = Cfg::XFORM, WIDE = Cfg::WIDE;
   constexpr int KBW = Cfg::KBW;
   // k-split tail tiles: 1/rms must come from outside (a slice sees only part of a row) and the epilogue is plain
   constexpr bool TAIL = PRESTATS && !SWIGLU && BN == 256;
@@ -230,8 +241,15 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             tma_load_2d_pair(sbase + Cfg::OFF_A + s * Cfg::A_BYTES, extra ? &tm_x2 : &tm_x, lead_ready, kcol,
                              mt * 256 + (int)rank * 128);
           }
-          tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, extra ? &tm_w2 : &tm_w, lead_ready, kcol,
-                           SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
+          if (WIDE) {
+            // two boxes of 128 weight rows: this CTA's share of the tile's first and second 256 columns
+            tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kcol, nt * BN + (int)rank * 128);
+            tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES + Cfg::B_BYTES / 2, &tm_w, lead_ready, kcol,
+                             nt * BN + 256 + (int)rank * 128);
+          } else {
+            tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, extra ? &tm_w2 : &tm_w, lead_ready, kcol,
+                             SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
+          }
         }
         __syncwarp();
         if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -240,7 +258,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer (rank 0 only)
     if (rank == 0) {
-      constexpr uint32_t idesc = FP8 ? make_idesc(256, BN, 0, 0) : make_idesc(256, BN, 1, 1);
+      constexpr uint32_t idesc = FP8 ? make_idesc(256, Cfg::MMA_N, 0, 0) : make_idesc(256, Cfg::MMA_N, 1, 1);
       const uint32_t leader = (lane == 0) ? 1u : 0u;
       const uint64_t bdesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_B);
       const uint64_t adesc0 = make_sw128_kmajor_desc(sbase + Cfg::OFF_A);
@@ -249,8 +267,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       bool ok = true;
       PairItem w;
       for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
-        const int acc = (NACC == 2) ? (it & 1) : 0;
-        const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+        // (WIDE: every tile uses both column halves, barrier set 0 for the first and 1 for the second)
+        const int acc = WIDE ? 0 : ((NACC == 2) ? (it & 1) : 0);
+        const uint32_t aph = (NACC == 2 && !WIDE) ? ((it >> 1) & 1) : (it & 1);
         if (!mbar_wait_warp(bar_tempty(acc), aph ^ 1u, ctl, 1, 3 * STAGES + NACC + acc, it)) break;
         const uint32_t d = tmem_base + acc * BN;
         // The issue loop sets the tensor cores' pace: one barrier wait per k-block, the poll for the
@@ -271,6 +290,19 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             umma_kblock_f8_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
                                    bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != w.kb0),
                                    bar_empty(s), leader);
+          } else if (WIDE) {
+            const uint64_t ad = adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4));
+            const uint64_t bd = bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4));
+            umma_kblock_ss_pair_nocommit(d, ad, bd, idesc, (uint32_t)(kb != w.kb0), leader);
+            if (kb == w.kb0) {
+              // the second half may still be draining the tile before: its MMAs wait for that, the first half's
+              // are already running
+              if (!mbar_wait_warp(bar_tempty(1), aph ^ 1u, ctl, 1, 3 * STAGES + NACC + 1, it)) { ok = false; break; }
+              tc_fence_after();
+            }
+            umma_kblock_ss_pair_nocommit(d + 256, ad, bd + (uint64_t)((Cfg::B_BYTES / 2) >> 4), idesc,
+                                         (uint32_t)(kb != w.kb0), leader);
+            umma_commit_pair_pred(bar_empty(s), leader);
           } else {
             umma_kblock_ss_pair(d, adesc0 + (uint64_t)(s * (Cfg::A_BYTES >> 4)),
                                 bdesc0 + (uint64_t)(s * (Cfg::B_BYTES >> 4)), idesc, (uint32_t)(kb != w.kb0), bar_empty(s),
@@ -388,8 +420,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     for (int it = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, it, w); ++it) {
       int mt, nt;
       prefill_tile_coords(w.t, p, mt, nt);
-      const int acc = (NACC == 2) ? (it & 1) : 0;
-      const uint32_t aph = (NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      const int acc = WIDE ? 0 : ((NACC == 2) ? (it & 1) : 0);
+      const uint32_t aph = (NACC == 2 && !WIDE) ? ((it >> 1) & 1) : (it & 1);
       [[maybe_unused]] const float* wc_tile = wsc + (it & 1) * 256;
       if (FP8) {
         // stage this tile's 256 per-channel scales while the accumulator is still filling; the buffer of the
@@ -675,11 +707,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           tmem_ld32(trow + c * 64, v0);
           tmem_ld32(trow + c * 64 + 32, v1);
           tmem_wait_ld();
-          if (c == BN / 64 - 1) {
-            // accumulator drained into registers: the pair's MMA warp may start on it again
+          if (c == BN / 64 - 1 || (WIDE && c == 3)) {
+            // accumulator (WIDE: this half of it) drained into registers: the pair's MMA warp may start on it again
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+            if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * (WIDE ? (c > 3 ? 1 : 0) : acc));
           }
           uint32_t lo[16], hi[16];
           cvt32(v0, lo, c * 64);

@@ -461,6 +461,25 @@ __device__ __forceinline__ void umma_kblock_ss_pair(uint32_t d_tmem, uint64_t ad
       : "memory");
 }
 
+// The four K = 16 steps of one k-block without the commit: for tiles made of two MMA-wide column halves, where the
+// ring slot is released after both halves have been issued.
+__device__ __forceinline__ void umma_kblock_ss_pair_nocommit(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                             uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b1, b2, b3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "add.u64 b1, %2, 2;\n\tadd.u64 b2, %2, 4;\n\tadd.u64 b3, %2, 6;\n\t"
+      "add.u64 a1, %1, 2;\n\tadd.u64 a2, %1, 4;\n\tadd.u64 a3, %1, 6;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a1, b1, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a2, b2, %3, p;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], a3, b3, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+
 // e4m3 x e4m3 -> fp32 pair MMA, one k-block of 128 elements (four K = 32 steps) plus the commit.
 __device__ __forceinline__ void umma_kblock_f8_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                        uint32_t accumulate, uint32_t commit_bar, uint32_t leader) {

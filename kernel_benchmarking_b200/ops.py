@@ -135,7 +135,7 @@ def rmsnorm_linear(x: torch.Tensor, gamma: Optional[torch.Tensor], W: torch.Tens
         return out
     with _on_device(x.device):
         nbytes = lib.rl_workspace_bytes(M, N, K, _lib.RL_W_BF16)
-        if v == _lib.VARIANTS["prefill_pair_prescaled"]:
+        if v in (_lib.VARIANTS["prefill_pair_prescaled"], _lib.VARIANTS["prefill_pair_wide"]):
             nbytes += M * K * 2 + 256  # room for the gamma-folded copy of x at widths where AUTO would not make one
         ws = _workspace(x.device, nbytes, stream)
         rc = lib.rl_rmsnorm_linear_bf16(

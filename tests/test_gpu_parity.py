@@ -66,7 +66,7 @@ def test_small_and_ragged_shapes(M, N, K, has_gamma):
 @pytest.mark.parametrize("variant", ["prefill_ts_n192", "prefill_ss_n192", "prefill_ss_n256", "prefill_ts_n128",
                                      "prefill_ss_n128", "prefill_pair_n256", "prefill_pair_n192",
                                      "prefill_pair_direct", "prefill_pair_prestats", "prefill_pair_direct_prestats",
-                                     "prefill_pair_prestats_whole", "prefill_pair_prescaled"])
+                                     "prefill_pair_prestats_whole", "prefill_pair_prescaled", "prefill_pair_wide"])
 @pytest.mark.parametrize("has_gamma", [False, True])
 @pytest.mark.parametrize("M,N,K", [(384, 776, 448), (1100, 2048, 1024)])
 def test_every_prefill_variant(variant, has_gamma, M, N, K):
@@ -687,6 +687,50 @@ def test_gamma_folded_by_the_pre_pass_gives_the_bits_of_the_main_loop_fold(M, N,
     xb[:, :K] = xd
     assert torch.equal(kb.rmsnorm_linear(xb[:, :K], gd, Wd, 1e-6, variant="prefill_pair_prescaled"), y_pre)
     kb.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 520, 328), (257, 700, 64), (512, 1032, 256), (1000, 8, 128), (2048, 7168, 1024)])
+@pytest.mark.parametrize("has_gamma", [False, True])
+def test_wide_tiles_give_the_bits_of_whole_narrow_tiles(M, N, K, has_gamma):
+    """256 x 512 tiles (two MMA-wide column halves sharing one activation tile) against 256 x 256 tiles computed
+    whole: the same k order per output element, so the same bits - including tiles whose second half, or whose
+    second half's tail, lies beyond N."""
+    x, gm, W = orc.make_inputs(M, N, K, seed=23, gamma=has_gamma)
+    xd, Wd = x.to(DEV), W.to(DEV)
+    gd = gm.to(DEV) if has_gamma else None
+    y_wide = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_wide")
+    narrow = "prefill_pair_prestats_whole" if has_gamma else "prefill_pair_direct_prestats"
+    y_narrow = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant=narrow)
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert orc.rel_max_err(y_wide.cpu(), orc.reference_fp32(x, gm, W, 1e-6)) <= BF16_TOL
+    # (without gamma the narrow kernel may cut its last round along K: one bf16 ulp there)
+    if has_gamma:
+        assert torch.equal(y_wide, y_narrow)
+    else:
+        assert orc.rel_max_err(y_wide, y_narrow.float()) <= ONE_ULP
+
+
+def test_auto_picks_wide_tiles_for_long_k_loops_that_fill_their_rounds():
+    lib = _lib.load()
+    name = lambda *a: _lib.VARIANT_NAMES[lib.rl_select_variant(*a)]
+    assert name(16384, 57344, 8192, 1, 1) == "prefill_pair_wide"      # the whole MLP layer: 97 rounds of wide tiles
+    assert name(16384, 7168, 8192, 1, 1) == "prefill_pair_wide"       # one of eight shards: 13 rounds beat 24.2 narrow ones
+    assert name(8192, 8192, 8192, 0, 1) == "prefill_pair_wide"        # without gamma as well
+    assert name(4096, 6144, 4096, 1, 1) == "prefill_pair_prescaled"   # 2.6 rounds of wide tiles would run as 3
+    assert name(4096, 28672, 2048, 1, 1) == "prefill_pair_prescaled"  # short k-loop: the drain of a wide tile shows
+    M, N, K = 2048, 18944, 4096                                       # 8 x 37 wide tiles = 4 rounds of 74 pairs
+    assert name(M, N, K, 1, 1) == "prefill_pair_wide"
+    assert name(M, N, K, 0, 1) == "prefill_pair_wide"
+    x, gm, W = orc.make_inputs(M, N, K, seed=24)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y = kb.rmsnorm_linear(xd, gd, Wd, 1e-6)
+    assert torch.equal(y, kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_wide"))
+    assert torch.equal(y, kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_prestats_whole"))
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    assert orc.rel_max_err(y, orc.reference_fp32(xd, gd, Wd, 1e-6)) <= BF16_TOL
 
 
 def test_auto_folds_gamma_in_the_pre_pass_only_when_the_workspace_holds_the_copy():
