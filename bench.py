@@ -54,6 +54,7 @@ WORKLOADS = {
     "decode_64x28672x4096": (64, 28672, 4096, "hbm", False),
     "mlp_shard8_16384x7168x8192": (16384, 7168, 8192, "tensor", False),
     "mlp_shard4_16384x14336x8192": (16384, 14336, 8192, "tensor", False),
+    "mlp_shard2_16384x28672x8192": (16384, 28672, 8192, "tensor", False),
     "bf16_8192x14336x4096": (8192, 14336, 4096, "tensor", False),
     "fp8w_8192x14336x4096": (8192, 14336, 4096, "tensor", True),   # e4m3 weights + per-channel scales
     "fp8w_decode_16x28672x4096": (16, 28672, 4096, "hbm", True),   # e4m3 weights at decode size: half the bytes
@@ -70,7 +71,13 @@ EXTRA_MULTI = ["fp8w_8192x14336x4096"]
 # DRAM bytes (read + written) per launch of the dominant kernel, from one profiler capture each, keyed by the
 # kernel variant and the per-GPU shape it was captured on.  A run whose variant or shape is not listed reports null.
 MEASURED_DRAM_BYTES = {
-    # the GEMM kernel on the gamma-folded copy of x; the pre-pass that writes the copy adds up to 4 M K bytes
+    # 256 x 512 tiles on the gamma-folded copy of x (what AUTO runs on the default workload and its column shards);
+    # the pre-pass that writes the copy adds up to 4 M K bytes
+    ("prefill_pair_wide", 16384, 7168, 8192): 2258.8e6,
+    ("prefill_pair_wide", 16384, 14336, 8192): 5276.3e6,
+    ("prefill_pair_wide", 16384, 28672, 8192): 12507.3e6,
+    ("prefill_pair_wide", 8192, 14336, 4096): 682.3e6,
+    # 256 x 256 tiles on the copy (by name on these shapes)
     ("prefill_pair_prescaled", 4096, 6144, 4096): 125.6e6,
     ("prefill_pair_prescaled", 16384, 7168, 8192): 2332.6e6,
     ("prefill_pair_prescaled", 16384, 14336, 8192): 4895.8e6,
@@ -84,9 +91,11 @@ MEASURED_DRAM_BYTES = {
     ("decode", 64, 28672, 4096): 242.4e6,
     ("e4m3 decode", 16, 28672, 4096): 122.0e6,
 }
-# The default workload's launches (3.1 GB on the device at N = 1) are too large to capture.  The two captures of its
-# column shards above show its traffic growing in proportion to the weight rows (x 2.10 for twice the rows), so a
-# shard of N rows is given the 7168-row capture's bytes times N / 7168, and the line says that it is scaled.
+# The default workload's launches (3.4 GB on the device at N = 1) are too large to capture.  With 256 x 256 tiles the
+# captures of its column shards grow in proportion to the weight rows (x 2.10 for twice the rows), so a shard of N
+# rows is given the 7168-row capture's bytes times N / 7168, and the line says that it is scaled.  With 256 x 512
+# tiles they grow faster (x 2.34 and x 2.37 per doubling: 2.26, 5.28, 12.5 GB for an eighth, a quarter and half of
+# the rows), so nothing is extrapolated and the whole layer on one GPU reports no figure.
 SCALED_FROM = {"prefill_pair_prescaled": ("prefill_pair_prescaled", 16384, 7168, 8192),
                "prefill_pair_prestats": ("prefill_pair_prestats", 16384, 7168, 8192)}
 
@@ -102,6 +111,9 @@ def dram_traffic(kernel, M, N, K):
         if (M, K) == (m0, kk0) and N % 256 == 0 and N > n0:
             return MEASURED_DRAM_BYTES[base] * N / n0, (f"scaled by N / {n0} from an ncu capture of {m0}x{n0}x{kk0} "
                                                         "(measured proportional to the weight rows)")
+    if (kernel, M, K) == ("prefill_pair_wide", 16384, 8192):
+        return None, ("too large to capture; the captures of its column shards (2.26, 5.28 and 12.5 GB for 7168, 14336 and "
+                      "28672 weight rows) grow faster than in proportion, so nothing is extrapolated")
     return None, "no capture for this kernel and shape"
 
 
