@@ -867,6 +867,9 @@ int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   pa.status = reinterpret_cast<int*>(workspace); pa.ws_bytes = workspace_bytes; pa.tail_off = wl.tail_off; pa.ws_total = wl.total;
   pa.sms = di.sms; pa.st = (cudaStream_t)stream;
   pa.no_norm = true;
+  int wide_pairs = 0;
+  if (max_cta_pairs<PairWide>(di.sms, &wide_pairs) == RL_OK && wide_tiles_pay(M, N, K, wide_pairs))
+    return launch_prefill_pair<PairWide>(pa);
   return launch_prefill_pair<PairDirect>(pa);
 }
 

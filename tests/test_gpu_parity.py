@@ -489,6 +489,19 @@ def test_plain_gemm_max_line(M, N, K):
     assert orc.rel_max_err(y.cpu(), ref) <= BF16_TOL
 
 
+def test_plain_gemm_on_wide_tiles():
+    """A shape whose 256 x 512 tiles fill their rounds (8 x 37 tiles = 4 rounds of 74 pairs): the norm-free GEMM
+    takes them too; full tensor against fp32 matmul on the GPU."""
+    M, N, K = 2048, 18944, 4096
+    x, _, W = orc.make_inputs(M, N, K, seed=41)
+    xd, Wd = x.to(DEV), W.to(DEV)
+    y = kb.gemm_nt(xd, Wd)
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    assert orc.rel_max_err(y, xd.float() @ Wd.float().t()) <= BF16_TOL
+
+
 def test_harness_job_runs_and_reports(tmp_path):
     """The reference-style job on its smallest shape: rows for b200 / torch / max, accuracy columns filled."""
     from kernel_benchmarking_b200 import harness
