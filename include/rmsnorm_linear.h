@@ -71,8 +71,8 @@ enum {
                                            (rl_workspace_bytes counts it for such shapes); by name for any shape, with M * K * 2 + 256
                                            bytes added to rl_workspace_bytes */
   RL_VARIANT_PREFILL_PAIR_WIDE = 18,     /* as 16 (gamma == NULL) or 17 (gamma != NULL) on 256 x 512 tiles: every pair reads half the
-                                           activation bytes per FLOP; every tile whole.  What AUTO runs in place of 16 / 17 for
-                                           K >= 4096 when the 512-column tiles fill their rounds */
+                                           activation bytes per FLOP; last round cut along K like 14's.  What AUTO runs in place of 16 / 17
+                                           for K >= 4096 when the 512-column tiles' rounds cost less than the 256-column tiles' */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
   RL_VARIANT_DECODE = 20,          /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
   RL_VARIANT_AUTO_WHOLE = 30       /* as AUTO, but never a kernel whose CTAs wait for one another (no k-split last round):

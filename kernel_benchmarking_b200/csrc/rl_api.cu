@@ -135,7 +135,7 @@ int device_info(DeviceInfo* out) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // fp32 partial blocks of k-split tail tiles: one 128 x 256 block per CTA of the persistent grid
-constexpr size_t TAIL_SLOT_BYTES = (size_t)128 * 256 * 4;
+constexpr size_t TAIL_SLOT_BYTES = (size_t)128 * 512 * 4;  // (the 512-column tiles' blocks; 256-column tiles use half)
 constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
 
 // Wide layers fold gamma into a copy of x once, in the row-statistics pre-pass, instead of in every column tile's
@@ -148,21 +148,6 @@ constexpr size_t TAIL_BYTES = (size_t)RL_MAX_CTAS * TAIL_SLOT_BYTES;
 // 512 x 14336 x 4096 and 1024 x 6144 x 4096 equal, 2048 x 8192 x 2048 5 % faster.
 constexpr int RL_PRESCALE_MIN_N = 6144;
 constexpr long long RL_PRESCALE_MIN_MNK = 30000000000ll;   // M N K: a GEMM of about 50 us
-// 256 x 512 tiles (PairWide) halve the activation bytes every pair pulls in and issue eight MMAs per barrier wait
-// instead of four: measured 6-10 % more work per unit of time than 256 x 256 tiles, tile for tile.  Their last round
-// is not cut along K, though, so they run in whole rounds of the resident pairs while the narrow tiles' k-split makes
-// that kernel's time nearly proportional to its tile count.  Wide tiles where the rounds they need, at 93 % of
-// the narrow tiles' time per column, come to less.
-inline bool wide_tiles_pay(int M, int N, int K, int pairs) {
-  if (K < 4096 || pairs <= 0) return false;
-  const long long m_tiles = (M + 255) / 256;
-  const long long tiles512 = m_tiles * ((N + 511) / 512), tiles256 = m_tiles * ((N + 255) / 256);
-  const long long rounds512 = (tiles512 + pairs - 1) / pairs;
-  if (rounds512 < 4) return false;
-  // time in units of one narrow tile: 2 x 0.93 per round of wide tiles; narrow tiles / pairs plus a quarter
-  // for the exchange of the k-split round
-  return 2.0 * 0.93 * (double)rounds512 < (double)tiles256 / pairs + 0.25;
-}
 inline bool prescale_pays(int M, int N, int K) {
   return N >= RL_PRESCALE_MIN_N && (long long)M * N * K >= RL_PRESCALE_MIN_MNK;
 }
@@ -281,6 +266,26 @@ TailPlan plan_tail(long long tiles, int max_pairs, int KB) {
   return TailPlan{0, 0};
 }
 
+// 256 x 512 tiles (PairWide) halve the activation bytes every pair pulls in and issue eight MMAs per barrier wait
+// instead of four: measured 6-10 % more work per unit of time than 256 x 256 tiles, tile for tile.  There are half as
+// many of them, so their last, partly filled round weighs twice as much.  Both widths are costed in units of one
+// narrow tile's time - whole rounds, plus the last round: nothing, a k-split's 1/S and the exchange (about 15
+// k-blocks), or a whole round when it cannot be split - and the wide tiles run where theirs, at 93 % per column,
+// comes to at least 2 % less.
+inline double rounds_cost(long long tiles, int pairs, int KB) {
+  const TailPlan tp = plan_tail(tiles, pairs, KB);
+  const double last = (tiles % pairs == 0) ? 0.0 : (tp.split > 1 ? 1.0 / tp.split + 15.0 / KB : 1.0);
+  return (double)(tiles / pairs) + last;
+}
+inline bool wide_tiles_pay(int M, int N, int K, int pairs) {
+  if (K < 4096 || pairs <= 0) return false;
+  const long long m_tiles = (M + 255) / 256;
+  const long long tiles512 = m_tiles * ((N + 511) / 512), tiles256 = m_tiles * ((N + 255) / 256);
+  if (tiles512 < 3LL * pairs) return false;
+  const int KB = (K + 63) / 64;
+  return 2.0 * 0.93 * rounds_cost(tiles512, pairs, KB) < 0.98 * rounds_cost(tiles256, pairs, KB);
+}
+
 // Row tiles (of 256 tokens) per sweep group.  Tiles are walked group by group, a group's row tiles against every
 // column tile, so the x rows of one group stay in L2 while W streams past; W is read from DRAM once per group.
 // Two limits.  The group's x rows must fit a budget well inside the 126 MB L2 (the W tiles in flight and the y
@@ -380,7 +385,7 @@ int launch_prefill_pair(const PairArgs& a) {
   if ((rc = max_cta_pairs<Cfg>(a.sms, &max_pairs))) return rc;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  if (Cfg::PRESTATS && !Cfg::SWIGLU && Cfg::BN == 256 && a.split_tail && a.status != nullptr) {
+  if (Cfg::PRESTATS && !Cfg::SWIGLU && (Cfg::BN == 256 || Cfg::BN == 512) && a.split_tail && a.status != nullptr) {
     const TailPlan tp = plan_tail(tiles, max_pairs, (K + Cfg::KBW - 1) / Cfg::KBW + p.extra_kb);
     if (tp.split > 1 && a.ws_total > 0 && a.ws_bytes >= a.ws_total) {
       p.tail_tiles = tp.tiles;

@@ -139,7 +139,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   constexpr bool FP8 = Cfg::FP8, XFORM = Cfg::XFORM, WIDE = Cfg::WIDE;
   constexpr int KBW = Cfg::KBW;
   // k-split tail tiles: 1/rms must come from outside (a slice sees only part of a row) and the epilogue is plain
-  constexpr bool TAIL = PRESTATS && !SWIGLU && BN == 256;
+  constexpr bool TAIL = PRESTATS && !SWIGLU && (BN == 256 || BN == 512);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
@@ -500,7 +500,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           unsigned* cnt = p.tail_counters + 2 * (tl * 2 + (int)rank);  // [0] partials written, [1] waits passed
           constexpr int SLOT_F4 = 128 * BN / 4;                        // float4 per (tile, slice, rank) block
           constexpr uint32_t PART_BYTES = 64 * 128 * 4;                // 64 columns of a block: contiguous
-          static_assert(4 * PART_BYTES <= (uint32_t)Cfg::OFF_EPI, "partial buffers ((S - 1) x chunks <= 4) fit in the operand ring");
+          // (S - 1) x the chunks a contributor finishes: at most 4 of a 256-column tile's four chunks, 6 of a
+          // 512-column tile's eight (S = 2: 4, S = 3: 2 x 3, S = 4: 3 x 2)
+          constexpr uint32_t PART_BUFS = (BN == 512) ? 6 : 4;
+          static_assert(PART_BUFS * PART_BYTES <= (uint32_t)Cfg::OFF_EPI, "partial buffers fit in the operand ring");
           // block layout [column / 4][row] float4: a warp's 32 rows of one column group are 512 contiguous bytes
           float4* slot0 = reinterpret_cast<float4*>(p.tail_partials) + (size_t)(tl * S * 2 + (int)rank) * SLOT_F4;
           float4* mine = slot0 + (size_t)w.slice * 2 * SLOT_F4;

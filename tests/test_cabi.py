@@ -42,9 +42,9 @@ def test_version_and_error_strings(lib):
 
 def test_workspace_bytes_is_pure_arithmetic(lib):
     small = lib.rl_workspace_bytes(4096, 4096, 4096, 0)
-    # status block + counter region + one 1/rms per token + one 128 x 256 fp32 partial block per CTA of the
-    # largest grid (160) for the k-split tiles of a partly filled last round
-    assert small == 256 + 65536 + 4096 * 4 + 160 * 128 * 256 * 4
+    # status block + counter region + one 1/rms per token + one 128 x 512 fp32 partial block per CTA of the
+    # largest grid (160) for the k-split tiles of a partly filled last round (256-column tiles use half of each)
+    assert small == 256 + 65536 + 4096 * 4 + 160 * 128 * 512 * 4
     # layers of 6144 channels and more: room for the gamma-folded copy of x [M, K] as well
     assert lib.rl_workspace_bytes(4096, 6144, 4096, 0) == small + 4096 * 4096 * 2
     assert lib.rl_workspace_bytes(4096, 6144 - 8, 4096, 0) == small

@@ -724,6 +724,28 @@ def test_wide_tiles_give_the_bits_of_whole_narrow_tiles(M, N, K, has_gamma):
         assert orc.rel_max_err(y_wide, y_narrow.float()) <= ONE_ULP
 
 
+@pytest.mark.parametrize("M,N,K,has_gamma", [(2048, 5120, 2048, True),      # 80 wide tiles = 74 + 6: the 6 cut in 4
+                                             (2304, 8192, 2560, False),     # 144 = 74 + 70: nothing to cut
+                                             (4608, 4608, 2048, True),      # 162 = 2 x 74 + 14: cut in 4
+                                             (2560, 6144, 3072, True)])     # 120 = 74 + 46: too many to cut
+def test_wide_tiles_split_their_last_round_along_k(M, N, K, has_gamma):
+    """The tiles of a partly filled last round of 256 x 512 tiles are cut along K like those of 256 x 256 tiles
+    (partial blocks of 128 x 512 per CTA): one bf16 ulp from tiles computed whole, same bits run to run."""
+    x, gm, W = orc.make_inputs(M, N, K, seed=27, gamma=has_gamma)
+    xd, Wd = x.to(DEV), W.to(DEV)
+    gd = gm.to(DEV) if has_gamma else None
+    y = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_wide")
+    y_again = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant="prefill_pair_wide")
+    narrow = "prefill_pair_prestats_whole" if has_gamma else "prefill_pair_direct_prestats"
+    y_narrow = kb.rmsnorm_linear(xd, gd, Wd, 1e-6, variant=narrow)
+    torch.cuda.synchronize()
+    kb.check_status()
+    assert torch.equal(y, y_again)
+    assert orc.rel_max_err(y, y_narrow.float()) <= ONE_ULP
+    torch.backends.cuda.matmul.allow_tf32 = False
+    assert orc.rel_max_err(y, orc.reference_fp32(xd, gd, Wd, 1e-6)) <= BF16_TOL
+
+
 def test_auto_picks_wide_tiles_for_long_k_loops_that_fill_their_rounds():
     lib = _lib.load()
     name = lambda *a: _lib.VARIANT_NAMES[lib.rl_select_variant(*a)]
