@@ -38,6 +38,12 @@ struct PrefillParams {
   float* tail_partials;
   int extra_kb;  // pair kernels: k-blocks appended from a second pair of operand matrices (0 or 1)
   int x_from_prepass;  // pair kernels: the activation matrix is written by the kernel launched just before (rowscale_kernel)
+  // Pair kernels: best-effort alignment of the resident pairs at tile boundaries (nullptr = off).  round_words[pair]
+  // holds (round_epoch << 12) | the index of the tile that pair has started (0xfff once it has none left); a pair
+  // about to start its i-th tile gives the others up to round_wait_ns to get there.  Timing only: nothing depends on it.
+  unsigned* round_words;
+  unsigned round_epoch;    // 20 bits, different for every launch
+  unsigned round_wait_ns;
 };
 
 // Row statistics on their own: rstd[m] = rsqrt(mean_k x[m,k]^2 + eps).  One warp per token row, 16-byte

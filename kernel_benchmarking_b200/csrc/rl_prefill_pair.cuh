@@ -221,6 +221,26 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     for (int i = 0; ok && pair_item<TAIL>(p, pair, n_pairs, total_tiles, KB, i, w); ++i) {
       int mt, nt;
       prefill_tile_coords(w.t, p, mt, nt);
+      if (p.round_words != nullptr && rank == 0 && i >= 1 && w.slice < 0) {
+        // Best-effort alignment.  Pairs that share an operand panel fetch each k-block of it from DRAM once only while
+        // they walk it together; left alone they drift apart over a long sweep (16384 x 28672 x 8192: 11.6 GB read,
+        // 5.8 GB with this).  Say that this pair starts its i-th tile, then give the others a moment to get there;
+        // whoever is not there by then is not waited for.
+        const unsigned want = (p.round_epoch << 12) | (unsigned)i;
+        if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.round_words + pair), "r"(want) : "memory");
+        const uint64_t t0 = global_timer_ns();
+        while (true) {
+          bool mine = true;
+          for (int j = lane; j < n_pairs; j += 32) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.round_words + j) : "memory");
+            mine = mine && ((v >> 12) == p.round_epoch) && ((v & 0xfffu) >= (unsigned)i);
+          }
+          if (__all_sync(0xffffffffu, mine)) break;
+          if (__any_sync(0xffffffffu, global_timer_ns() - t0 > (uint64_t)p.round_wait_ns)) break;
+          __nanosleep(100);
+        }
+      }
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         if (!mbar_wait_warp(bar_empty(s), ph ^ 1, ctl, 0, 2 * STAGES + s, kb)) { ok = false; break; }
         if (elect_one()) {
@@ -255,6 +275,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
+    if (p.round_words != nullptr && rank == 0 && lane == 0)
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.round_words + pair), "r"((p.round_epoch << 12) | 0xfffu) : "memory");
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer (rank 0 only)
     if (rank == 0) {
