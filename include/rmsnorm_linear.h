@@ -75,8 +75,9 @@ enum {
                                            for K >= 4096 when the 512-column tiles' rounds cost less than the 256-column tiles' */
   RL_VARIANT_PREFILL_PAIR_DIRECT = 11, /* CTA pairs, gamma == NULL only: x straight from shared memory, 256 x 256, two accumulators */
   RL_VARIANT_DECODE = 20,          /* M <= 64: operand-swapped, stream-K over (channel tile, k block) units */
-  RL_VARIANT_AUTO_WHOLE = 30       /* as AUTO, but never a kernel whose CTAs wait for one another (no k-split last round):
-                                      for callers that keep several launches in flight on one device */
+  RL_VARIANT_AUTO_WHOLE = 30       /* as AUTO, but never a kernel whose CTAs wait for one another (no k-split last round, no
+                                      alignment of the CTA pairs at tile boundaries): for callers that keep several launches
+                                      in flight on one device */
 };
 
 /* Library version (major * 1000 + minor).  No reference counterpart. */
