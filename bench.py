@@ -73,7 +73,7 @@ EXTRA_MULTI = ["fp8w_8192x14336x4096"]
 MEASURED_DRAM_BYTES = {
     # 256 x 512 tiles on the gamma-folded copy of x (what AUTO runs on the default workload and its column shards);
     # the pre-pass that writes the copy adds up to 4 M K bytes
-    ("prefill_pair_wide", 16384, 7168, 8192): 2258.8e6,
+    ("prefill_pair_wide", 16384, 7168, 8192): 2116.6e6,
     ("prefill_pair_wide", 16384, 14336, 8192): 5276.3e6,
     ("prefill_pair_wide", 16384, 28672, 8192): 6705.4e6,    # (12.5 GB before the pairs re-aligned at tile boundaries)
     ("prefill_pair_wide", 8192, 14336, 4096): 682.3e6,
@@ -94,7 +94,7 @@ MEASURED_DRAM_BYTES = {
 # The default workload's launches (3.4 GB on the device at N = 1) are too large to capture.  With 256 x 256 tiles the
 # captures of its column shards grow in proportion to the weight rows (x 2.10 for twice the rows), so a shard of N
 # rows is given the 7168-row capture's bytes times N / 7168, and the line says that it is scaled.  With 256 x 512
-# tiles they do not (2.26, 5.28 and 6.71 GB for an eighth, a quarter and half of the rows: the longer sweeps re-align
+# tiles they do not (2.12, 5.28 and 6.71 GB for an eighth, a quarter and half of the rows: the longer sweeps re-align
 # their pairs at tile boundaries, the shorter ones do not), so nothing is extrapolated and the whole layer on one GPU
 # reports no figure.
 SCALED_FROM = {"prefill_pair_prescaled": ("prefill_pair_prescaled", 16384, 7168, 8192),
@@ -113,7 +113,7 @@ def dram_traffic(kernel, M, N, K):
             return MEASURED_DRAM_BYTES[base] * N / n0, (f"scaled by N / {n0} from an ncu capture of {m0}x{n0}x{kk0} "
                                                         "(measured proportional to the weight rows)")
     if (kernel, M, K) == ("prefill_pair_wide", 16384, 8192):
-        return None, ("too large to capture; the captures of its column shards (2.26, 5.28 and 6.71 GB for 7168, 14336 and "
+        return None, ("too large to capture; the captures of its column shards (2.12, 5.28 and 6.71 GB for 7168, 14336 and "
                       "28672 weight rows) do not grow in proportion, so nothing is extrapolated")
     return None, "no capture for this kernel and shape"
 
