@@ -156,6 +156,9 @@ inline bool prescale_pays(int M, int N, int K) {
 #ifndef RL_ROUND_WAIT_NS
 #define RL_ROUND_WAIT_NS 50000u
 #endif
+#ifndef RL_ALIGN_MIN_ROUNDS
+#define RL_ALIGN_MIN_ROUNDS 32
+#endif
 constexpr size_t SYNC_BYTES = 1024;  // RL_MAX_CTAS / 2 progress words, rounded up
 struct WsLayout {
   size_t counters_off, ssq_off, partials_off, total;
@@ -406,10 +409,10 @@ int launch_prefill_pair(const PairArgs& a) {
   // Long sweeps of wide tiles (a workspace given, and the caller has not asked for kernels whose CTAs never wait):
   // the pairs re-align at tile boundaries, best effort, RL_ROUND_WAIT_NS at most per tile.  Measured: it halves
   // the DRAM reads of 16384 x 28672 x 8192 (48 rounds: 11.6 -> 5.8 GB, 1321 -> 1352 TFLOP/s sustained) and changes
-  // nothing at 12 rounds; on the 256 x 256 kernels, whose few rounds end in a k-split, it cost 2-6 % in bursts
+  // nothing at 12 rounds (24 rounds: +1 % sustained at K = 8192, -0.7 % at K = 4096); on the 256 x 256 kernels, whose few rounds end in a k-split, it cost 2-6 % in bursts
   // (pairs that start every tile together hit L2 together), so they run free.
   if (Cfg::WIDE && a.sync_off != 0 && a.split_tail && a.status != nullptr && a.ws_bytes >= a.sync_off + SYNC_BYTES &&
-      tiles >= 32LL * pairs && tiles / pairs < 4000) {
+      tiles >= (long long)RL_ALIGN_MIN_ROUNDS * pairs && tiles / pairs < 4000) {
     static std::atomic<unsigned> epoch_counter{0};
     p.round_words = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(a.status) + a.sync_off);
     p.round_epoch = (++epoch_counter) & 0xfffffu;
