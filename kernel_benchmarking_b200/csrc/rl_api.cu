@@ -202,6 +202,7 @@ using PairFoldN192 = PairCfg<192, 2, 6, 4, 2, A_TS_FOLD>;
 using PairDirectFused = PairCfg<256, 2, 6, 1, 2, A_SS_DIRECT>;     // no gamma: x straight from shared memory
 using PairDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true>;    // ... with 1/rms from the pre-pass (or no norm at all)
 using PairWide = PairCfg<512, 2, 4, 1, 0, A_SS_DIRECT, true>;      // the same on 256 x 512 tiles: half the x bytes per FLOP
+using PairSwigluWide = PairCfg<512, 2, 4, 1, 0, A_SS_DIRECT, true, true>;  // 256 output channels per tile: 256 gate + 256 up columns
 using PairSwiglu = PairCfg<256, 1, 6, 6, 2, A_TS_FOLD, true, true>;
 using PairSwigluDirect = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, true>;  // no gamma, or gamma folded by the pre-pass
 using PairFp8 = PairCfg<256, 2, 6, 1, 0, A_SS_DIRECT, true, false, true>;
@@ -372,7 +373,8 @@ int launch_prefill_pair(const PairArgs& a) {
   p.gamma = prescale ? nullptr : a.gamma;
   p.x_from_prepass = prescale ? 1 : 0;
   p.m_tiles = (M + 255) / 256;
-  p.n_tiles = Cfg::SWIGLU ? (N + 127) / 128 : (N + Cfg::BN - 1) / Cfg::BN;  // SwiGLU: N = output channels, W has 2N rows
+  // SwiGLU: N = output channels, W has 2N rows; a tile covers half as many output channels as it has accumulator columns
+  p.n_tiles = Cfg::SWIGLU ? (N + Cfg::BN / 2 - 1) / (Cfg::BN / 2) : (N + Cfg::BN - 1) / Cfg::BN;
   p.group_m = pick_group_m(p.m_tiles, (long long)256 * K * eb);
   p.status = a.status;
   p.extra_kb = (a.x2 != nullptr) ? 1 : 0;
@@ -869,12 +871,19 @@ int rl_rmsnorm_swiglu_bf16(const void* x, const void* gamma, const void* W, void
   pa.sms = di.sms; pa.st = (cudaStream_t)stream;
   // without gamma there is nothing to fold: x straight from shared memory.  With gamma the same kernel runs on the
   // copy the pre-pass folds it into, where the layer is wide enough to pay for the copy and the workspace holds it.
-  if (gamma == nullptr) return launch_prefill_pair<PairSwigluDirect>(pa);
-  if (wl.xs_bytes > 0 && workspace_bytes >= wl.total) {
-    pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
-    return launch_prefill_pair<PairSwigluDirect>(pa);
+  const bool folded_copy = gamma != nullptr && wl.xs_bytes > 0 && workspace_bytes >= wl.total;
+  if (gamma != nullptr && !folded_copy) return launch_prefill_pair<PairSwiglu>(pa);
+  if (folded_copy) pa.xs = reinterpret_cast<uint8_t*>(workspace) + wl.xs_off;
+  // 256 x 512 tiles where their whole rounds (neither width cuts its last round here) cost clearly less
+  int pairs = 0;
+  if (K >= 4096 && max_cta_pairs<PairSwigluWide>(di.sms, &pairs) == RL_OK && pairs > 0) {
+    const long long m_tiles = (M + 255) / 256;
+    const long long t_wide = m_tiles * ((N + 255) / 256), t_narrow = m_tiles * ((N + 127) / 128);
+    const long long r_wide = (t_wide + pairs - 1) / pairs, r_narrow = (t_narrow + pairs - 1) / pairs;
+    if (t_wide >= 3LL * pairs && 2.0 * 0.93 * (double)r_wide < 0.98 * (double)r_narrow)
+      return launch_prefill_pair<PairSwigluWide>(pa);
   }
-  return launch_prefill_pair<PairSwiglu>(pa);
+  return launch_prefill_pair<PairSwigluDirect>(pa);
 }
 
 int rl_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,

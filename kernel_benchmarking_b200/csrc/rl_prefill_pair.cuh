@@ -44,7 +44,8 @@ struct PairCfg {
   // loads gate channels, the rank-1 CTA the matching up channels, so accumulator columns [0,128) and
   // [128,256) hold gate and up of the same 128 output channels and the epilogue emits silu(gate) * up.
   static constexpr bool SWIGLU = SWIGLU_;
-  static_assert(!SWIGLU_ || BN_ == 256, "SwiGLU epilogue: 256-column tile (gate and up halves)");
+  // (BN = 512: the tile's first 256 accumulator columns are gate, the second 256 up, of the same 256 output channels)
+  static_assert(!SWIGLU_ || BN_ == 256 || BN_ == 512, "SwiGLU epilogue: gate and up halves of 128 or 256 columns");
   // FP8: both operands are e4m3 (activations quantised per token by rowquant_kernel, weights with per-channel
   // scales), k-blocks of 128 elements (the same 128 bytes per tile row), kind::f8f6f4 MMAs, and the epilogue
   // multiplies by row_scale[m] * w_scale[n].
@@ -58,7 +59,7 @@ struct PairCfg {
   // is still draining.  Each CTA's W stage is two boxes of 128 rows, one per half.
   static constexpr bool WIDE = (BN_ == 512);
   static constexpr int MMA_N = WIDE ? 256 : BN_;
-  static_assert(!WIDE || (NACC_ == 2 && AMODE_ == A_SS_DIRECT && PRESTATS_ && !FP8_ && !SWIGLU_),
+  static_assert(!WIDE || (NACC_ == 2 && AMODE_ == A_SS_DIRECT && PRESTATS_ && !FP8_),
                 "512-column tiles: transform-free bf16, two separately released halves");
   // XFORM: the kernel has transform warps (they fold gamma and / or accumulate the sums of squares).  Without
   // them (x straight from shared memory, 1/rms from the pre-pass) both operand tiles complete directly on the
@@ -263,9 +264,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           }
           if (WIDE) {
             // two boxes of 128 weight rows: this CTA's share of the tile's first and second 256 columns
-            tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kcol, nt * BN + (int)rank * 128);
+            // (SwiGLU: the first half is this CTA's 128 gate channels of the tile's 256, the second the matching up channels)
+            tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, &tm_w, lead_ready, kcol,
+                             SWIGLU ? nt * 256 + (int)rank * 128 : nt * BN + (int)rank * 128);
             tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES + Cfg::B_BYTES / 2, &tm_w, lead_ready, kcol,
-                             nt * BN + 256 + (int)rank * 128);
+                             SWIGLU ? p.N + nt * 256 + (int)rank * 128 : nt * BN + 256 + (int)rank * 128);
           } else {
             tma_load_2d_pair(sbase + Cfg::OFF_B + s * Cfg::B_BYTES, extra ? &tm_w2 : &tm_w, lead_ready, kcol,
                              SWIGLU ? (int)rank * p.N + nt * 128 : nt * BN + (int)rank * (BN / 2));
@@ -635,6 +638,47 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       }
       if (tail_done) {
         // the slice's columns were finished above
+      } else if constexpr (SWIGLU && WIDE) {
+        // p.N = n output channels; this tile covers channels nt*256 .. +255: gate in columns [0,256), up in [256,512).
+        // Four chunks of 64 output channels through the two staging tiles; both halves are free after the last read.
+        const int m0 = mt * 256 + (int)rank * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c, ++chunk_no) {
+          uint8_t* stage = smem + Cfg::OFF_EPI + (chunk_no & 1) * Cfg::EPI_BYTES;
+          if (epi_tid == 0) tma_store_wait_read<1>();
+          named_bar_sync(1, 128);
+          uint32_t lo[16], hi[16];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t vg[32], vu[32];
+            tmem_ld32(trow + c * 64 + h * 32, vg);
+            tmem_ld32(trow + 256 + c * 64 + h * 32, vu);
+            tmem_wait_ld();
+            uint32_t (&o)[16] = (h == 0) ? lo : hi;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(vg[2 * j]) * r, g1 = __uint_as_float(vg[2 * j + 1]) * r;
+              const float u0 = __uint_as_float(vu[2 * j]) * r, u1 = __uint_as_float(vu[2 * j + 1]) * r;
+              o[j] = pack_bf16x2(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+            }
+          }
+          if (c == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive_cluster(lead_tempty0);
+              mbar_arrive_cluster(lead_tempty0 + 8u);
+            }
+          }
+          sts64(stage, lo, hi);
+          fence_proxy_async_smem();
+          named_bar_sync(2, 128);
+          if (epi_tid == 0) {
+            const int n0 = nt * 256 + c * 64;
+            if (n0 < p.N) tma_store_2d_hint(&tm_y, smem_u32(stage), n0, m0, pol_y);
+            tma_store_commit();
+          }
+        }
       } else if constexpr (SWIGLU) {
         // p.N = n output channels; this tile covers channels nt*128 .. +127: gate in columns [0,128), up in [128,256)
         uint8_t* stage0 = smem + Cfg::OFF_EPI;

@@ -561,6 +561,31 @@ def test_swiglu_wide_layers_fold_gamma_in_the_pre_pass():
     assert torch.equal(y2, y)
 
 
+def test_swiglu_on_wide_tiles():
+    """A SwiGLU layer whose 256 x 512 tiles (256 gate + 256 up columns of the same 256 output channels) fill four
+    rounds: same bits as the 256-column tiles (reached here through a workspace without room for the folded copy,
+    which folds gamma in the main loop), and the whole tensor against fp32 torch on the GPU."""
+    import ctypes
+    lib = _lib.load()
+    M, n, K = 2048, 9472, 4096
+    x, gm, W = orc.make_inputs(M, 2 * n, K, seed=33)
+    xd, gd, Wd = x.to(DEV), gm.to(DEV), W.to(DEV)
+    y = kb.rmsnorm_swiglu(xd, gd, Wd, 1e-6)
+    y_nogamma = kb.rmsnorm_swiglu(xd, None, Wd, 1e-6)
+    torch.cuda.synchronize()
+    kb.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    assert orc.rel_max_err(y, orc.torch_rmsnorm_swiglu(xd.float(), gd.float(), Wd.float(), 1e-6)) <= BF16_TOL
+    assert orc.rel_max_err(y_nogamma, orc.torch_rmsnorm_swiglu(xd.float(), None, Wd.float(), 1e-6)) <= BF16_TOL
+    ws = torch.zeros(lib.rl_workspace_bytes(M, n, K, _lib.RL_W_BF16) - M * K * 2, dtype=torch.uint8, device=DEV)
+    y2 = torch.empty(M, n, dtype=torch.bfloat16, device=DEV)
+    rc = lib.rl_rmsnorm_swiglu_bf16(xd.data_ptr(), gd.data_ptr(), Wd.data_ptr(), y2.data_ptr(), M, n, K, K, K, n,
+                                    ctypes.c_float(1e-6), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
+
+
 def test_lora_golden_and_shapes(golden_dir):
     """LoRA-fused linear (the low-rank term as one more k-block of the main loop) against the reference's
     `torch_lora` output and, on larger shapes, against the restatement in fp32 on the GPU."""
