@@ -73,6 +73,7 @@ EXTRA_MULTI = ["fp8w_8192x14336x4096"]
 MEASURED_DRAM_BYTES = {
     # 256 x 512 tiles on the gamma-folded copy of x (what AUTO runs on the default workload and its column shards);
     # the pre-pass that writes the copy adds up to 4 M K bytes
+    ("prefill_pair_wide", 16384, 57344, 8192): 13150.0e6,   # the two DRAM byte counters alone: a one-pass capture, taken at full size
     ("prefill_pair_wide", 16384, 7168, 8192): 2116.6e6,
     ("prefill_pair_wide", 16384, 14336, 8192): 5276.3e6,
     ("prefill_pair_wide", 16384, 28672, 8192): 6705.4e6,    # (12.5 GB before the pairs re-aligned at tile boundaries)
@@ -91,12 +92,11 @@ MEASURED_DRAM_BYTES = {
     ("decode", 64, 28672, 4096): 242.4e6,
     ("e4m3 decode", 16, 28672, 4096): 122.0e6,
 }
-# The default workload's launches (3.4 GB on the device at N = 1) are too large to capture.  With 256 x 256 tiles the
-# captures of its column shards grow in proportion to the weight rows (x 2.10 for twice the rows), so a shard of N
-# rows is given the 7168-row capture's bytes times N / 7168, and the line says that it is scaled.  With 256 x 512
-# tiles they do not (2.12, 5.28 and 6.71 GB for an eighth, a quarter and half of the rows: the longer sweeps re-align
-# their pairs at tile boundaries, the shorter ones do not), so nothing is extrapolated and the whole layer on one GPU
-# reports no figure.
+# The default workload's launches (3.4 GB on the device at N = 1) are too large for a multi-pass capture; the two DRAM
+# byte counters on their own are one pass and were taken on it directly (13.15 GB per launch on 256 x 512 tiles).
+# For the 256 x 256 kernels, which AUTO no longer runs on that shape, the captures of its column shards grow in
+# proportion to the weight rows (x 2.10 for twice the rows), so a shard of N rows is given the 7168-row capture's
+# bytes times N / 7168, and the line says that it is scaled.
 SCALED_FROM = {"prefill_pair_prescaled": ("prefill_pair_prescaled", 16384, 7168, 8192),
                "prefill_pair_prestats": ("prefill_pair_prestats", 16384, 7168, 8192)}
 
@@ -112,9 +112,6 @@ def dram_traffic(kernel, M, N, K):
         if (M, K) == (m0, kk0) and N % 256 == 0 and N > n0:
             return MEASURED_DRAM_BYTES[base] * N / n0, (f"scaled by N / {n0} from an ncu capture of {m0}x{n0}x{kk0} "
                                                         "(measured proportional to the weight rows)")
-    if (kernel, M, K) == ("prefill_pair_wide", 16384, 8192):
-        return None, ("too large to capture; the captures of its column shards (2.12, 5.28 and 6.71 GB for 7168, 14336 and "
-                      "28672 weight rows) do not grow in proportion, so nothing is extrapolated")
     return None, "no capture for this kernel and shape"
 
 
